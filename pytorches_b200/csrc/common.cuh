@@ -1,0 +1,82 @@
+// Internal declarations shared by the plugin's translation units: launch plumbing, exact integer
+// division for index math, and the launcher entry points the boundary (plugin.cu) dispatches to.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstddef>
+#include <cstdint>
+
+namespace b200 {
+
+// Coalesced dims a kernel accepts (after dropping size-1 dims and merging contiguous neighbours).
+constexpr int MAX_DIMS = 8;
+
+// Number of kernels launched by this library since load (reported through the extension API).
+extern std::atomic<uint64_t> g_kernel_launches;
+
+// B200 has 148 SMs; grids of persistent kernels are sized from the queried count at run time.
+int sm_count(int device);
+
+// Exact floor division by a runtime constant. For 32-bit operands: Lemire's method,
+// floor(n/d) = hi64(ceil(2^64/d) * n) for every n, d < 2^32 (d > 1). For 64-bit operands the
+// hardware-emulated division is used; that path only runs for tensors of 2^32 or more work items.
+template <typename I> struct Divider;
+template <> struct Divider<uint32_t> {
+    uint64_t magic;
+    uint32_t d;
+    Divider() : magic(0), d(1) {}
+    explicit Divider(uint64_t d_) : magic(d_ > 1 ? UINT64_MAX / d_ + 1 : 0), d((uint32_t)d_) {}
+    __device__ __forceinline__ void divmod(uint32_t n, uint32_t &q, uint32_t &r) const {
+        q = d == 1 ? n : (uint32_t)__umul64hi(magic, (uint64_t)n);
+        r = n - q * d;
+    }
+};
+template <> struct Divider<uint64_t> {
+    uint64_t d;
+    Divider() : d(1) {}
+    explicit Divider(uint64_t d_) : d(d_) {}
+    __device__ __forceinline__ void divmod(uint64_t n, uint64_t &q, uint64_t &r) const {
+        q = n / d;
+        r = n - q * d;
+    }
+};
+
+// One coalesced dimension of an elementwise op: its size and each operand's element stride.
+struct EwDim {
+    uint64_t size;
+    uint64_t stride[2];
+};
+
+// Elementwise problem after host-side coalescing (reference: plugins/cpu/src/ew.rs:22-43).
+struct EwProblem {
+    int nd = 0;          // coalesced dims, outermost first; 0 means a single element
+    EwDim dim[MAX_DIMS];
+    uint64_t n = 1;      // output elements
+};
+
+// ---- launchers (each enqueues on `s` and returns the CUDA error of the launch) --------------------
+cudaError_t launch_unary(uint32_t op, const float *x, float *out, const EwProblem &p, cudaStream_t s);
+cudaError_t launch_binary(uint32_t op, const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s);
+cudaError_t launch_axpy(const float *a, const float *b, float *out, float alpha, uint64_t n, cudaStream_t s);
+cudaError_t launch_fill(float *out, uint64_t n, float v, cudaStream_t s);
+cudaError_t launch_randn(float *out, uint64_t n, uint64_t seed, cudaStream_t s);
+cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const float *b, uint64_t brs, uint64_t bcs,
+                          float *c, uint64_t m, uint64_t n, uint64_t k, cudaStream_t s);
+
+// Reductions over the middle axis of a contiguous (outer, len, inner) tensor. `scratch` must hold
+// reduce_scratch_bytes(...) bytes (0 means none is needed); it is global memory the kernels use for
+// per-block partial results between their two passes.
+enum ReduceKind : int { REDUCE_SUM = 0, REDUCE_MAX = 1, REDUCE_ARGMAX = 2 };
+size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
+cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, void *out,
+                          void *scratch, int device, cudaStream_t s);
+
+}  // namespace b200
+
+// Counts and checks one kernel launch.
+#define B200_LAUNCH(kernel, grid, block, smem, stream, ...)                         \
+    do {                                                                            \
+        kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);                 \
+        ::b200::g_kernel_launches.fetch_add(1, std::memory_order_relaxed);          \
+    } while (0)

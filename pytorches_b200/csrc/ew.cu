@@ -1,0 +1,652 @@
+// Elementwise kernels of the B200 plugin: unary ops, binary ops with N-d strided broadcasting,
+// AXPY, FILL, RAND_NORMAL. They take the place of plugins/cpu/src/ew.rs in the reference CPU plugin.
+//
+// All of this is HBM-bound streaming work, so the design is about bytes in flight, not math:
+//   * 128-bit (float4) coalesced accesses; every thread issues all loads of its UNROLL work items
+//     before the first use, so a CTA keeps BLOCK*UNROLL*16 bytes per operand in flight;
+//   * a "flat" kernel for fully contiguous operands (and scalar broadcasts);
+//   * a "rows" kernel for everything whose innermost coalesced dim has operand strides 0 or 1: the
+//     work item is one float4 of one row; the row number is split over the outer dims with exact
+//     multiply-high division, and the dim tables travel in the kernel's constant parameter bank;
+//   * a "tile" kernel for operands whose unit stride sits in another dim than the output's
+//     (transposed views): 32x32 tiles go through padded shared memory so both sides stay coalesced;
+//   * a generic gather kernel for whatever is left.
+// Outputs are always contiguous (docs/plugin-abi.md:169). Buffers start on 256-byte boundaries
+// (handles are never offset by the host, docs/plugin-abi.md:119-122), so float4 access at a multiple
+// of 4 elements is always aligned.
+//
+// Arithmetic is one IEEE operation per element, written with the __f*_rn intrinsics so that no
+// multiply-add contraction can change bits relative to the reference.
+#include "common.cuh"
+#include "vecmath.cuh"
+
+namespace b200 {
+
+namespace {
+
+enum : uint32_t {
+    OP_NEG = 1, OP_EXP = 2, OP_LOG = 3, OP_RELU = 4, OP_TANH = 5, OP_STEP = 6,
+    OP_ADD = 100, OP_SUB = 101, OP_MUL = 102, OP_DIV = 103, OP_COPY = 300,
+};
+
+// ---- per-element functors ------------------------------------------------------------------------
+// Unary semantics follow plugins/cpu/src/ew.rs:96-106 (RELU is max(v, 0) with NaN -> 0; STEP is v > 0).
+template <uint32_t OP> struct UnaryFn;
+template <> struct UnaryFn<OP_NEG> { __device__ __forceinline__ static float f(float v) { return -v; } };
+template <> struct UnaryFn<OP_RELU> { __device__ __forceinline__ static float f(float v) { return v > 0.0f ? v : 0.0f; } };
+template <> struct UnaryFn<OP_STEP> { __device__ __forceinline__ static float f(float v) { return v > 0.0f ? 1.0f : 0.0f; } };
+template <> struct UnaryFn<OP_EXP> { __device__ __forceinline__ static float f(float v) { return exp_ref(v); } };
+template <> struct UnaryFn<OP_LOG> { __device__ __forceinline__ static float f(float v) { return log_ref(v); } };
+template <> struct UnaryFn<OP_TANH> { __device__ __forceinline__ static float f(float v) { return tanh_ref(v); } };
+template <> struct UnaryFn<OP_COPY> { __device__ __forceinline__ static float f(float v) { return v; } };
+
+template <uint32_t OP> struct BinaryFn;
+template <> struct BinaryFn<OP_ADD> { __device__ __forceinline__ static float f(float a, float b) { return __fadd_rn(a, b); } };
+template <> struct BinaryFn<OP_SUB> { __device__ __forceinline__ static float f(float a, float b) { return __fsub_rn(a, b); } };
+template <> struct BinaryFn<OP_MUL> { __device__ __forceinline__ static float f(float a, float b) { return __fmul_rn(a, b); } };
+template <> struct BinaryFn<OP_DIV> { __device__ __forceinline__ static float f(float a, float b) { return __fdiv_rn(a, b); } };
+
+// ---- memory access helpers --------------------------------------------------------------------------
+// Inputs are read once: bypass L1 allocation. Outputs are written once: streaming stores.
+__device__ __forceinline__ float4 ld4(const float *p) { return __ldcs(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float ld1(const float *p) { return __ldcs(p); }
+__device__ __forceinline__ void st4(float *p, float4 v) { __stcs(reinterpret_cast<float4 *>(p), v); }
+__device__ __forceinline__ void st1(float *p, float v) { __stcs(p, v); }
+
+constexpr int EW_BLOCK = 256;
+constexpr int EW_UNROLL = 4;
+
+// Grid for a kernel whose CTAs each take BLOCK*UNROLL work items.
+inline unsigned tiles_for(uint64_t items, int per_cta) { return (unsigned)((items + per_cta - 1) / per_cta); }
+
+// ---- flat kernels: contiguous operands, optional scalar broadcast ------------------------------------
+// MODE 0: out[i] = f(a[i], b[i]);  1: f(a[i], b[0]);  2: f(a[0], b[i]);  3: f(a[0], b[0]).
+// A work item is 4 consecutive elements; the last item may be partial and is done element by element.
+template <class Fn, int MODE>
+__global__ void __launch_bounds__(EW_BLOCK) binary_flat_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                                               float *__restrict__ out, uint64_t n) {
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
+    float4 va[EW_UNROLL], vb[EW_UNROLL];
+    float sa = 0.0f, sb = 0.0f;
+    if (MODE & 2) sa = a[0];
+    if (MODE & 1) sb = b[0];
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w < items && (w << 2) + 4 <= n) {
+            if (!(MODE & 2)) va[k] = ld4(a + (w << 2));
+            if (!(MODE & 1)) vb[k] = ld4(b + (w << 2));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w >= items) continue;
+        const uint64_t i = w << 2;
+        if (i + 4 <= n) {
+            const float4 x = (MODE & 2) ? make_float4(sa, sa, sa, sa) : va[k];
+            const float4 y = (MODE & 1) ? make_float4(sb, sb, sb, sb) : vb[k];
+            st4(out + i, make_float4(Fn::f(x.x, y.x), Fn::f(x.y, y.y), Fn::f(x.z, y.z), Fn::f(x.w, y.w)));
+        } else {
+            for (uint64_t j = i; j < n; ++j) out[j] = Fn::f((MODE & 2) ? sa : a[j], (MODE & 1) ? sb : b[j]);
+        }
+    }
+}
+
+template <class Fn>
+__global__ void __launch_bounds__(EW_BLOCK) unary_flat_kernel(const float *__restrict__ x, float *__restrict__ out, uint64_t n) {
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
+    float4 v[EW_UNROLL];
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w < items && (w << 2) + 4 <= n) v[k] = ld4(x + (w << 2));
+    }
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w >= items) continue;
+        const uint64_t i = w << 2;
+        if (i + 4 <= n) {
+            st4(out + i, make_float4(Fn::f(v[k].x), Fn::f(v[k].y), Fn::f(v[k].z), Fn::f(v[k].w)));
+        } else {
+            for (uint64_t j = i; j < n; ++j) out[j] = Fn::f(x[j]);
+        }
+    }
+}
+
+// ---- rows kernel: innermost strides in {0,1}, any outer strides --------------------------------------
+// Work item w = (row, c): row over the outer dims, c over the inner dim in steps of VEC elements.
+// NOPS operands (1 = unary, 2 = binary). I = uint32_t while the item count fits, else uint64_t.
+template <typename I, int NOPS> struct RowsPlan {
+    I items;                       // rows * cols
+    I inner;                       // elements in the innermost dim
+    Divider<I> cols;               // items per row = ceil(inner / VEC)
+    int n_outer;                   // outer dims (>= 1), listed innermost-outer first
+    Divider<I> outer[MAX_DIMS];    // their sizes (the last listed, outermost, is never divided by)
+    uint64_t ostride[NOPS][MAX_DIMS];
+    uint32_t istride[NOPS];        // 0 or 1
+};
+
+template <typename I, int NOPS>
+__device__ __forceinline__ void rows_offsets(const RowsPlan<I, NOPS> &p, I row, uint64_t (&off)[NOPS]) {
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) off[o] = 0;
+    for (int d = 0; d < p.n_outer - 1; ++d) {
+        I q, r;
+        p.outer[d].divmod(row, q, r);
+        row = q;
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) off[o] += (uint64_t)r * p.ostride[o][d];
+    }
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) off[o] += (uint64_t)row * p.ostride[o][p.n_outer - 1];
+}
+
+template <typename I, int VEC> struct Pack;
+template <typename I> struct Pack<I, 4> {
+    float4 v;
+    __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) {
+        if (istride) v = ld4(base + (uint64_t)c * 4);
+        else { const float s = *base; v = make_float4(s, s, s, s); }
+    }
+};
+template <typename I> struct Pack<I, 1> {
+    float v;
+    __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) { v = istride ? ld1(base + c) : *base; }
+};
+
+template <class Fn, typename I, int VEC>
+__global__ void __launch_bounds__(EW_BLOCK) binary_rows_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                                               float *__restrict__ out,
+                                                               const __grid_constant__ RowsPlan<I, 2> p) {
+    const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
+    Pack<I, VEC> va[EW_UNROLL], vb[EW_UNROLL];
+    uint64_t oo[EW_UNROLL];
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const I w = tile + (I)(k * EW_BLOCK);
+        if (w < p.items) {
+            I row, c;
+            p.cols.divmod(w, row, c);
+            uint64_t off[2];
+            rows_offsets<I, 2>(p, row, off);
+            va[k].load(a + off[0], p.istride[0], c);
+            vb[k].load(b + off[1], p.istride[1], c);
+            oo[k] = (uint64_t)row * p.inner + (uint64_t)c * VEC;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const I w = tile + (I)(k * EW_BLOCK);
+        if (w < p.items) {
+            if constexpr (VEC == 4) {
+                const float4 x = va[k].v, y = vb[k].v;
+                st4(out + oo[k], make_float4(Fn::f(x.x, y.x), Fn::f(x.y, y.y), Fn::f(x.z, y.z), Fn::f(x.w, y.w)));
+            } else {
+                st1(out + oo[k], Fn::f(va[k].v, vb[k].v));
+            }
+        }
+    }
+}
+
+template <class Fn, typename I, int VEC>
+__global__ void __launch_bounds__(EW_BLOCK) unary_rows_kernel(const float *__restrict__ x, float *__restrict__ out,
+                                                              const __grid_constant__ RowsPlan<I, 1> p) {
+    const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
+    Pack<I, VEC> v[EW_UNROLL];
+    uint64_t oo[EW_UNROLL];
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const I w = tile + (I)(k * EW_BLOCK);
+        if (w < p.items) {
+            I row, c;
+            p.cols.divmod(w, row, c);
+            uint64_t off[1];
+            rows_offsets<I, 1>(p, row, off);
+            v[k].load(x + off[0], p.istride[0], c);
+            oo[k] = (uint64_t)row * p.inner + (uint64_t)c * VEC;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const I w = tile + (I)(k * EW_BLOCK);
+        if (w < p.items) {
+            if constexpr (VEC == 4) {
+                const float4 t = v[k].v;
+                st4(out + oo[k], make_float4(Fn::f(t.x), Fn::f(t.y), Fn::f(t.z), Fn::f(t.w)));
+            } else {
+                st1(out + oo[k], Fn::f(v[k].v));
+            }
+        }
+    }
+}
+
+// ---- tile kernel: an operand whose unit stride lies in a non-innermost dim --------------------------
+// The output's innermost dim is I (size ni); dim F (size nf) is where a "transposed" operand has
+// stride 1. A CTA handles a 32(F) x 32(I) tile of one batch entry (all other dims). Transposed
+// operands are read coalesced along F into padded shared memory and consumed along I; "direct"
+// operands (inner stride 0 or 1) are read in output orientation. Output writes are coalesced along I.
+template <int NOPS> struct TilePlan {
+    uint32_t nf, ni;               // sizes of dims F and I
+    uint32_t tiles_f, tiles_i;
+    uint64_t out_fstride;          // output stride of dim F (dim I has stride 1)
+    int n_batch;                   // remaining dims, listed innermost first
+    Divider<uint64_t> batch[MAX_DIMS];
+    uint64_t out_bstride[MAX_DIMS];
+    uint64_t bstride[NOPS][MAX_DIMS];
+    uint64_t fstride[NOPS], istride[NOPS];
+    uint32_t transposed[NOPS];     // 1: via shared memory (fstride == 1)
+};
+
+constexpr int TILE = 32;
+constexpr int TILE_ROWS = 8;  // CTA is 32 x 8 threads
+
+template <class Fn, int NOPS>
+__global__ void __launch_bounds__(TILE *TILE_ROWS) tile_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                                               float *__restrict__ out,
+                                                               const __grid_constant__ TilePlan<NOPS> p) {
+    __shared__ float sm[NOPS][TILE][TILE + 1];
+    const float *src[2] = {a, b};
+    // blockIdx.x enumerates (batch, tile_f, tile_i) with tile_i fastest.
+    uint64_t t = blockIdx.x;
+    const uint32_t ti = (uint32_t)(t % p.tiles_i);
+    t /= p.tiles_i;
+    const uint32_t tf = (uint32_t)(t % p.tiles_f);
+    uint64_t bidx = t / p.tiles_f;
+    uint64_t boff[NOPS], oboff = 0;
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) boff[o] = 0;
+    for (int d = 0; d < p.n_batch; ++d) {
+        uint64_t q, r;
+        p.batch[d].divmod(bidx, q, r);
+        bidx = q;
+        oboff += r * p.out_bstride[d];
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) boff[o] += r * p.bstride[o][d];
+    }
+    const uint32_t f0 = tf * TILE, i0 = ti * TILE;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    // Stage transposed operands: thread (tx, ty) reads element (f = f0 + tx, i = i0 + ty + 8k).
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) {
+        if (p.transposed[o]) {
+#pragma unroll
+            for (int k = 0; k < TILE; k += TILE_ROWS) {
+                const uint32_t f = f0 + tx, i = i0 + ty + k;
+                if (f < p.nf && i < p.ni) sm[o][ty + k][tx] = src[o][boff[o] + (uint64_t)f * p.fstride[o] + (uint64_t)i * p.istride[o]];
+            }
+        }
+    }
+    __syncthreads();
+    // Consume: thread (tx, ty) produces element (f = f0 + ty + 8k, i = i0 + tx).
+#pragma unroll
+    for (int k = 0; k < TILE; k += TILE_ROWS) {
+        const uint32_t f = f0 + ty + k, i = i0 + tx;
+        if (f < p.nf && i < p.ni) {
+            float v[NOPS];
+#pragma unroll
+            for (int o = 0; o < NOPS; ++o)
+                v[o] = p.transposed[o] ? sm[o][tx][ty + k] : src[o][boff[o] + (uint64_t)f * p.fstride[o] + (uint64_t)i * p.istride[o]];
+            float r;
+            if constexpr (NOPS == 2) r = Fn::f(v[0], v[1]);
+            else r = Fn::f(v[0]);
+            out[oboff + (uint64_t)f * p.out_fstride + i] = r;
+        }
+    }
+}
+
+// ---- generic gather kernel: any strides, one element per thread --------------------------------------
+template <int NOPS> struct GatherPlan {
+    uint64_t n;
+    int nd;                        // dims listed innermost first
+    Divider<uint64_t> size[MAX_DIMS];
+    uint64_t stride[NOPS][MAX_DIMS];
+};
+
+template <class Fn, int NOPS>
+__global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                                          float *__restrict__ out, const __grid_constant__ GatherPlan<NOPS> p) {
+    const uint64_t i = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
+    if (i >= p.n) return;
+    uint64_t rem = i, off[NOPS];
+#pragma unroll
+    for (int o = 0; o < NOPS; ++o) off[o] = 0;
+    for (int d = 0; d < p.nd; ++d) {
+        uint64_t q, r;
+        p.size[d].divmod(rem, q, r);
+        rem = q;
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) off[o] += r * p.stride[o][d];
+    }
+    if constexpr (NOPS == 2) out[i] = Fn::f(a[off[0]], b[off[1]]);
+    else out[i] = Fn::f(a[off[0]]);
+}
+
+// ---- AXPY, FILL, RAND_NORMAL --------------------------------------------------------------------------
+// out = a + alpha*b. The reference fuses the multiply-add (one rounding) for every element except
+// the last n mod 8, which it computes with two roundings (plugins/cpu/src/ew.rs:316-329; its chunks
+// of 65536 are multiples of 8, so only the global tail is unfused). `out` may alias `a`.
+__global__ void __launch_bounds__(EW_BLOCK) axpy_kernel(const float *a, const float *b, float *out, float alpha, uint64_t n) {
+    const uint64_t n_fused = n - (n & 7);
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
+    float4 va[EW_UNROLL], vb[EW_UNROLL];
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w < items && (w << 2) + 4 <= n) {
+            va[k] = ld4(a + (w << 2));
+            vb[k] = ld4(b + (w << 2));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w >= items) continue;
+        const uint64_t i = w << 2;
+        if (i + 4 <= n) {
+            const float4 x = va[k], y = vb[k];
+            float4 r;
+            if (i < n_fused) {
+                r = make_float4(__fmaf_rn(alpha, y.x, x.x), __fmaf_rn(alpha, y.y, x.y), __fmaf_rn(alpha, y.z, x.z), __fmaf_rn(alpha, y.w, x.w));
+            } else {
+                r = make_float4(__fadd_rn(x.x, __fmul_rn(alpha, y.x)), __fadd_rn(x.y, __fmul_rn(alpha, y.y)),
+                                __fadd_rn(x.z, __fmul_rn(alpha, y.z)), __fadd_rn(x.w, __fmul_rn(alpha, y.w)));
+            }
+            st4(out + i, r);
+        } else {
+            for (uint64_t j = i; j < n; ++j)
+                out[j] = j < n_fused ? __fmaf_rn(alpha, b[j], a[j]) : __fadd_rn(a[j], __fmul_rn(alpha, b[j]));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(EW_BLOCK) fill_kernel(float *__restrict__ out, uint64_t n, float v) {
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < EW_UNROLL; ++k) {
+        const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
+        if (w >= items) continue;
+        const uint64_t i = w << 2;
+        if (i + 4 <= n) st4(out + i, make_float4(v, v, v, v));
+        else for (uint64_t j = i; j < n; ++j) out[j] = v;
+    }
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+// The counter-based Box-Muller recipe of crates/plugin-abi/src/lib.rs:99-107. The integer hash is
+// exact; ln/cos come from CUDA's math library and may differ from the CPU's libm in the last ulp.
+__device__ __forceinline__ float rand_normal(uint64_t seed, uint64_t i) {
+    const uint64_t h = splitmix64(seed ^ (i * 0x9E3779B97F4A7C15ull));
+    const float u1 = __fdiv_rn((float)((h >> 40) + 1), 16777216.0f);
+    const float u2 = __fdiv_rn((float)(h & 0xFFFFFFull), 16777216.0f);
+    const float rad = sqrtf(__fmul_rn(-2.0f, logf(u1)));
+    const float ang = __fmul_rn(__fmul_rn(2.0f, 3.14159265358979323846264338327950288f), u2);
+    return __fmul_rn(rad, cosf(ang));
+}
+
+__global__ void __launch_bounds__(EW_BLOCK) randn_kernel(float *__restrict__ out, uint64_t n, uint64_t seed) {
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t w = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
+    if (w >= items) return;
+    const uint64_t i = w << 2;
+    if (i + 4 <= n) {
+        st4(out + i, make_float4(rand_normal(seed, i), rand_normal(seed, i + 1), rand_normal(seed, i + 2), rand_normal(seed, i + 3)));
+    } else {
+        for (uint64_t j = i; j < n; ++j) out[j] = rand_normal(seed, j);
+    }
+}
+
+// ---- required MATMUL: correctness only, outside the measured path --------------------------------------
+// 32x32 shared-memory tiles, k in order with one fused multiply-add per step; any operand strides.
+__global__ void __launch_bounds__(TILE *TILE) matmul_kernel(const float *__restrict__ a, uint64_t ars, uint64_t acs,
+                                                             const float *__restrict__ b, uint64_t brs, uint64_t bcs,
+                                                             float *__restrict__ c, uint64_t m, uint64_t n, uint64_t k) {
+    __shared__ float sa[TILE][TILE + 1], sb[TILE][TILE + 1];
+    const uint64_t row = (uint64_t)blockIdx.y * TILE + threadIdx.y, col = (uint64_t)blockIdx.x * TILE + threadIdx.x;
+    float acc = 0.0f;
+    for (uint64_t k0 = 0; k0 < k; k0 += TILE) {
+        const uint64_t ka = k0 + threadIdx.x, kb = k0 + threadIdx.y;
+        sa[threadIdx.y][threadIdx.x] = (row < m && ka < k) ? a[row * ars + ka * acs] : 0.0f;
+        sb[threadIdx.y][threadIdx.x] = (kb < k && col < n) ? b[kb * brs + col * bcs] : 0.0f;
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < TILE; ++p) acc = __fmaf_rn(sa[threadIdx.y][p], sb[p][threadIdx.x], acc);
+        __syncthreads();
+    }
+    if (row < m && col < n) c[row * n + col] = acc;
+}
+
+// ---- host side: choose a kernel for a coalesced problem --------------------------------------------
+
+template <int NOPS> bool inner_is_unit_or_zero(const EwProblem &p) {
+    for (int o = 0; o < NOPS; ++o)
+        if (p.dim[p.nd - 1].stride[o] > 1) return false;
+    return true;
+}
+
+template <typename I, int NOPS> RowsPlan<I, NOPS> make_rows_plan(const EwProblem &p, int vec) {
+    RowsPlan<I, NOPS> r{};
+    const EwDim &in = p.dim[p.nd - 1];
+    const uint64_t cols = (in.size + vec - 1) / vec;
+    r.inner = (I)in.size;
+    r.cols = Divider<I>(cols);
+    r.n_outer = p.nd - 1;
+    uint64_t rows = 1;
+    for (int d = 0; d < r.n_outer; ++d) {
+        const EwDim &od = p.dim[p.nd - 2 - d];  // innermost-outer first
+        r.outer[d] = Divider<I>(od.size);
+        for (int o = 0; o < NOPS; ++o) r.ostride[o][d] = od.stride[o];
+        rows *= od.size;
+    }
+    for (int o = 0; o < NOPS; ++o) r.istride[o] = (uint32_t)in.stride[o];
+    r.items = (I)(rows * cols);
+    return r;
+}
+
+// float4 access needs: inner size a multiple of 4 and, for operands read with inner stride 1, every
+// outer stride a multiple of 4 (row starts stay 16-byte aligned).
+template <int NOPS> int rows_vec_width(const EwProblem &p) {
+    const EwDim &in = p.dim[p.nd - 1];
+    if (in.size % 4) return 1;
+    for (int o = 0; o < NOPS; ++o) {
+        if (in.stride[o] != 1) continue;
+        for (int d = 0; d < p.nd - 1; ++d)
+            if (p.dim[d].stride[o] % 4) return 1;
+    }
+    return 4;
+}
+
+// Finds the dim (other than the innermost) in which operand o has stride 1, or -1.
+int unit_stride_dim(const EwProblem &p, int o) {
+    for (int d = 0; d < p.nd - 1; ++d)
+        if (p.dim[d].stride[o] == 1 && p.dim[d].size > 1) return d;
+    return -1;
+}
+
+// Tries to express the problem for the tile kernel. Every operand must be either "direct" (inner
+// stride 0 or 1) or "transposed" with its unit stride in one common dim F.
+template <int NOPS> bool make_tile_plan(const EwProblem &p, TilePlan<NOPS> &t, uint64_t &ctas) {
+    if (p.nd < 2) return false;
+    int F = -1;
+    for (int o = 0; o < NOPS; ++o) {
+        const uint64_t is = p.dim[p.nd - 1].stride[o];
+        if (is <= 1) { t.transposed[o] = 0; continue; }
+        const int f = unit_stride_dim(p, o);
+        if (f < 0 || (F >= 0 && f != F)) return false;
+        F = f;
+        t.transposed[o] = 1;
+    }
+    if (F < 0) return false;
+    const EwDim &df = p.dim[F], &di = p.dim[p.nd - 1];
+    if (df.size > UINT32_MAX || di.size > UINT32_MAX) return false;
+    t.nf = (uint32_t)df.size;
+    t.ni = (uint32_t)di.size;
+    t.tiles_f = (t.nf + TILE - 1) / TILE;
+    t.tiles_i = (t.ni + TILE - 1) / TILE;
+    // Output strides: contiguous over the coalesced dims.
+    uint64_t ostride[MAX_DIMS], acc = 1;
+    for (int d = p.nd - 1; d >= 0; --d) { ostride[d] = acc; acc *= p.dim[d].size; }
+    t.out_fstride = ostride[F];
+    for (int o = 0; o < NOPS; ++o) { t.fstride[o] = df.stride[o]; t.istride[o] = di.stride[o]; }
+    t.n_batch = 0;
+    uint64_t batches = 1;
+    for (int d = p.nd - 2; d >= 0; --d) {
+        if (d == F) continue;
+        const int j = t.n_batch++;
+        t.batch[j] = Divider<uint64_t>(p.dim[d].size);
+        t.out_bstride[j] = ostride[d];
+        for (int o = 0; o < NOPS; ++o) t.bstride[o][j] = p.dim[d].stride[o];
+        batches *= p.dim[d].size;
+    }
+    ctas = batches * t.tiles_f * t.tiles_i;
+    return ctas <= 0x7fffffffull;
+}
+
+template <int NOPS> GatherPlan<NOPS> make_gather_plan(const EwProblem &p) {
+    GatherPlan<NOPS> g{};
+    g.n = p.n;
+    g.nd = p.nd;
+    for (int d = 0; d < p.nd; ++d) {
+        const EwDim &src = p.dim[p.nd - 1 - d];
+        g.size[d] = Divider<uint64_t>(src.size);
+        for (int o = 0; o < NOPS; ++o) g.stride[o][d] = src.stride[o];
+    }
+    return g;
+}
+
+template <class Fn> cudaError_t run_binary(const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s) {
+    // Flat: one dim (or none) and inner strides in {0,1}.
+    if (p.nd <= 1) {
+        const uint64_t sa = p.nd ? p.dim[0].stride[0] : 0, sb = p.nd ? p.dim[0].stride[1] : 0;
+        if (sa <= 1 && sb <= 1) {
+            const unsigned grid = tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL);
+            const int mode = (sa ? 0 : 2) | (sb ? 0 : 1);
+            switch (mode) {
+                case 0: B200_LAUNCH((binary_flat_kernel<Fn, 0>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                case 1: B200_LAUNCH((binary_flat_kernel<Fn, 1>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                case 2: B200_LAUNCH((binary_flat_kernel<Fn, 2>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                default: B200_LAUNCH((binary_flat_kernel<Fn, 3>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+            }
+            return cudaGetLastError();
+        }
+    } else if (inner_is_unit_or_zero<2>(p)) {
+        const int vec = rows_vec_width<2>(p);
+        uint64_t rows = p.n / p.dim[p.nd - 1].size;
+        const uint64_t items = rows * ((p.dim[p.nd - 1].size + vec - 1) / vec);
+        const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
+        if (items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32)) {
+            auto plan = make_rows_plan<uint32_t, 2>(p, vec);
+            if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+        } else {
+            auto plan = make_rows_plan<uint64_t, 2>(p, vec);
+            if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+        }
+        return cudaGetLastError();
+    } else {
+        TilePlan<2> t{};
+        uint64_t ctas = 0;
+        if (make_tile_plan<2>(p, t, ctas)) {
+            B200_LAUNCH((tile_kernel<Fn, 2>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, a, b, out, t);
+            return cudaGetLastError();
+        }
+    }
+    auto g = make_gather_plan<2>(p);
+    B200_LAUNCH((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g);
+    return cudaGetLastError();
+}
+
+template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwProblem &p, cudaStream_t s) {
+    if (p.nd <= 1 && (p.nd == 0 || p.dim[0].stride[0] == 1)) {
+        B200_LAUNCH((unary_flat_kernel<Fn>), tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, x, out, p.n);
+        return cudaGetLastError();
+    }
+    if (p.nd >= 2 && inner_is_unit_or_zero<1>(p)) {
+        const int vec = rows_vec_width<1>(p);
+        const uint64_t rows = p.n / p.dim[p.nd - 1].size;
+        const uint64_t items = rows * ((p.dim[p.nd - 1].size + vec - 1) / vec);
+        const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
+        if (items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32)) {
+            auto plan = make_rows_plan<uint32_t, 1>(p, vec);
+            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan);
+            else B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan);
+        } else {
+            auto plan = make_rows_plan<uint64_t, 1>(p, vec);
+            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan);
+            else B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan);
+        }
+        return cudaGetLastError();
+    }
+    if (p.nd >= 2) {
+        TilePlan<1> t{};
+        uint64_t ctas = 0;
+        if (make_tile_plan<1>(p, t, ctas)) {
+            B200_LAUNCH((tile_kernel<Fn, 1>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, x, nullptr, out, t);
+            return cudaGetLastError();
+        }
+    }
+    auto g = make_gather_plan<1>(p);
+    B200_LAUNCH((gather_kernel<Fn, 1>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, x, nullptr, out, g);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_unary(uint32_t op, const float *x, float *out, const EwProblem &p, cudaStream_t s) {
+    switch (op) {
+        case OP_NEG: return run_unary<UnaryFn<OP_NEG>>(x, out, p, s);
+        case OP_EXP: return run_unary<UnaryFn<OP_EXP>>(x, out, p, s);
+        case OP_LOG: return run_unary<UnaryFn<OP_LOG>>(x, out, p, s);
+        case OP_RELU: return run_unary<UnaryFn<OP_RELU>>(x, out, p, s);
+        case OP_TANH: return run_unary<UnaryFn<OP_TANH>>(x, out, p, s);
+        case OP_STEP: return run_unary<UnaryFn<OP_STEP>>(x, out, p, s);
+        case OP_COPY: return run_unary<UnaryFn<OP_COPY>>(x, out, p, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_binary(uint32_t op, const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s) {
+    switch (op) {
+        case OP_ADD: return run_binary<BinaryFn<OP_ADD>>(a, b, out, p, s);
+        case OP_SUB: return run_binary<BinaryFn<OP_SUB>>(a, b, out, p, s);
+        case OP_MUL: return run_binary<BinaryFn<OP_MUL>>(a, b, out, p, s);
+        case OP_DIV: return run_binary<BinaryFn<OP_DIV>>(a, b, out, p, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t launch_axpy(const float *a, const float *b, float *out, float alpha, uint64_t n, cudaStream_t s) {
+    B200_LAUNCH(axpy_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, a, b, out, alpha, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill(float *out, uint64_t n, float v, cudaStream_t s) {
+    B200_LAUNCH(fill_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, out, n, v);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_randn(float *out, uint64_t n, uint64_t seed, cudaStream_t s) {
+    B200_LAUNCH(randn_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const float *b, uint64_t brs, uint64_t bcs, float *c,
+                          uint64_t m, uint64_t n, uint64_t k, cudaStream_t s) {
+    const dim3 grid((unsigned)((n + TILE - 1) / TILE), (unsigned)((m + TILE - 1) / TILE));
+    B200_LAUNCH(matmul_kernel, grid, dim3(TILE, TILE), 0, s, a, ars, acs, b, brs, bcs, c, m, n, k);
+    return cudaGetLastError();
+}
+
+}  // namespace b200

@@ -1,0 +1,559 @@
+// pytorches_plugin_b200: the C-ABI boundary of the B200 backend.
+//
+// Implements the pytorches plugin vtable (crates/plugin-abi/src/lib.rs:152-191, restated in
+// include/pytorches_plugin_abi.h) over the kernels in ew.cu and reduce.cu. It mirrors the behaviour of
+// the reference CPU plugin's boundary, plugins/cpu/src/lib.rs: argument validation and status codes
+// (lib.rs:250-334), a size-bucketed cache of freed buffers (lib.rs:36-134), and "never unwind across
+// the boundary" (lib.rs:345-352). What differs is what a GPU needs:
+//   * one in-order CUDA stream per device is the ABI's "implicit default stream"
+//     (docs/plugin-abi.md:142-158): execute and host-to-device copies enqueue and return, copy_to_host
+//     and synchronize block, and a freed buffer can be handed out again at once because its next use
+//     is ordered behind its last one on the same stream (docs/plugin-abi.md:133-135);
+//   * the CUDA runtime is linked statically and loads the driver lazily, so loading this library and
+//     calling device_count on a machine without a GPU or driver quietly reports zero devices
+//     (docs/plugin-abi.md:104-108);
+//   * there is no CPU fallback of any kind: without a usable GPU the plugin has no devices.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/pytorches_b200_ext.h"
+#include "../../include/pytorches_plugin_abi.h"
+#include "common.cuh"
+
+namespace b200 {
+
+std::atomic<uint64_t> g_kernel_launches{0};
+
+namespace {
+
+constexpr int MAX_DEVICES = 16;
+
+thread_local char g_err[512] = "b200: no error";
+
+void set_err(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+struct DeviceState {
+    std::mutex mu;                 // serialises calls into one device (docs/plugin-abi.md:232-233)
+    bool ready = false;
+    cudaStream_t stream = nullptr;
+    int sms = 0;
+    size_t total_mem = 0;
+    std::unordered_map<size_t, std::vector<void *>> free_by_size;  // cached blocks per bucket
+    std::unordered_map<void *, size_t> live;                      // handed-out blocks -> bucket
+    size_t cached_bytes = 0;
+    cudaError_t deferred = cudaSuccess;  // a fault seen after its call had already returned OK
+};
+
+DeviceState g_dev[MAX_DEVICES];
+std::once_flag g_count_once;
+int g_count = 0;
+
+int visible_devices() {
+    std::call_once(g_count_once, [] {
+        int n = 0;
+        // Fails (without printing) when there is no driver or no GPU: zero devices, not an error.
+        if (cudaGetDeviceCount(&n) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        g_count = n > MAX_DEVICES ? MAX_DEVICES : n;
+    });
+    return g_count;
+}
+
+// Makes `device` current on the calling thread and sets it up on first use. Call with d.mu held.
+cudaError_t ensure_device(uint32_t device) {
+    DeviceState &d = g_dev[device];
+    cudaError_t e = cudaSetDevice((int)device);
+    if (e != cudaSuccess) return e;
+    if (d.ready) return cudaSuccess;
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, (int)device)) != cudaSuccess) return e;
+    if ((e = cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    d.sms = prop.multiProcessorCount;
+    d.total_mem = prop.totalGlobalMem;
+    d.ready = true;
+    return cudaSuccess;
+}
+
+PtStatus cuda_fail(const char *what, cudaError_t e) {
+    set_err("b200: %s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+    (void)cudaGetLastError();
+    return e == cudaErrorMemoryAllocation ? PT_STATUS_OUT_OF_MEMORY : PT_STATUS_INTERNAL;
+}
+
+// ---- memory -------------------------------------------------------------------------------------------------
+
+// Same buckets as the reference (plugins/cpu/src/lib.rs:37-40): powers of two below 1 MiB (at least
+// 256 bytes here, the alignment cudaMalloc gives), 2 MiB steps above.
+size_t bucket(size_t bytes) {
+    constexpr size_t MIB = size_t(1) << 20;
+    if (bytes < MIB) {
+        size_t p = 256;
+        while (p < bytes) p <<= 1;
+        return p;
+    }
+    return (bytes + 2 * MIB - 1) / (2 * MIB) * (2 * MIB);
+}
+
+void flush_cache(DeviceState &d) {
+    for (auto &kv : d.free_by_size)
+        for (void *p : kv.second) (void)cudaFree(p);
+    d.free_by_size.clear();
+    d.cached_bytes = 0;
+}
+
+// Allocation under d.mu with the device current. Reuses a cached block of the same bucket; on
+// failure gives the cache back to the driver and retries once (docs/plugin-abi.md:129-130).
+PtStatus alloc_locked(DeviceState &d, size_t bytes, void **out) {
+    if (bytes > d.total_mem) {  // docs/plugin-abi.md:126-128: fail fast, stay usable
+        set_err("b200: alloc of %zu bytes: out of memory (device has %zu bytes)", bytes, d.total_mem);
+        return PT_STATUS_OUT_OF_MEMORY;
+    }
+    const size_t size = bucket(bytes);
+    auto it = d.free_by_size.find(size);
+    if (it != d.free_by_size.end() && !it->second.empty()) {
+        *out = it->second.back();
+        it->second.pop_back();
+        d.cached_bytes -= size;
+        d.live[*out] = size;
+        return PT_STATUS_OK;
+    }
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, size);
+    if (e == cudaErrorMemoryAllocation) {
+        (void)cudaGetLastError();
+        // Cached blocks may still be in use by queued work: wait for it before returning them.
+        (void)cudaStreamSynchronize(d.stream);
+        flush_cache(d);
+        e = cudaMalloc(&p, size);
+    }
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_err("b200: alloc of %zu bytes: cudaMalloc of %zu bytes: %s", bytes, size, cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? PT_STATUS_OUT_OF_MEMORY : PT_STATUS_INTERNAL;
+    }
+    d.live[p] = size;
+    *out = p;
+    return PT_STATUS_OK;
+}
+
+void free_locked(DeviceState &d, void *ptr) {
+    auto it = d.live.find(ptr);
+    if (it == d.live.end()) return;  // not ours, or freed twice: ignore rather than corrupt the cache
+    const size_t size = it->second;
+    d.live.erase(it);
+    // Keep at most half of the device cached; beyond that give blocks back. cudaFree waits for the
+    // device, so queued work that still uses the block finishes first.
+    if (d.cached_bytes + size > d.total_mem / 2) {
+        (void)cudaFree(ptr);
+        return;
+    }
+    d.free_by_size[size].push_back(ptr);
+    d.cached_bytes += size;
+}
+
+bool valid_device(uint32_t device) { return (int)device < visible_devices(); }
+
+#define B200_ENTER(device)                                                    \
+    if (!valid_device(device)) {                                              \
+        set_err("b200: device %u does not exist", (unsigned)(device));        \
+        return PT_STATUS_INVALID_ARGUMENT;                                    \
+    }                                                                         \
+    DeviceState &d = g_dev[device];                                           \
+    std::lock_guard<std::mutex> lock(d.mu);                                   \
+    if (cudaError_t e_ = ensure_device(device); e_ != cudaSuccess) return cuda_fail("device setup", e_)
+
+PtStatus alloc_buf(uint32_t device, size_t bytes, void **out) {
+    try {
+        if (!out) return PT_STATUS_INVALID_ARGUMENT;
+        B200_ENTER(device);
+        return alloc_locked(d, bytes, out);
+    } catch (...) {
+        set_err("b200: alloc raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+void free_buf(uint32_t device, void *ptr) {
+    try {
+        if (!ptr || !valid_device(device)) return;
+        DeviceState &d = g_dev[device];
+        std::lock_guard<std::mutex> lock(d.mu);
+        if (ensure_device(device) != cudaSuccess) return;
+        free_locked(d, ptr);
+    } catch (...) {
+    }
+}
+
+// A deferred fault is reported by the next call that can (docs/plugin-abi.md:155-156).
+PtStatus finish_blocking(DeviceState &d, const char *what) {
+    cudaError_t e = cudaStreamSynchronize(d.stream);
+    if (e == cudaSuccess && d.deferred != cudaSuccess) {
+        e = d.deferred;
+        d.deferred = cudaSuccess;
+    }
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail(what, e);
+}
+
+PtStatus copy_from_host(uint32_t device, void *dst, const void *src, size_t bytes) {
+    try {
+        B200_ENTER(device);
+        if (bytes == 0) return PT_STATUS_OK;
+        cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d.stream);
+        if (e != cudaSuccess) return cuda_fail("copy_from_host", e);
+        // The source is only the caller's for the duration of this call. Pageable memory has been
+        // staged by the time cudaMemcpyAsync returns; pinned memory is read by the DMA engine later,
+        // so wait for it.
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, src) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return finish_blocking(d, "copy_from_host");
+        }
+        if (attr.type != cudaMemoryTypeUnregistered) return finish_blocking(d, "copy_from_host");
+        return PT_STATUS_OK;
+    } catch (...) {
+        set_err("b200: copy_from_host raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+PtStatus copy_to_host(uint32_t device, void *dst, const void *src, size_t bytes) {
+    try {
+        B200_ENTER(device);
+        if (bytes) {
+            cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, d.stream);
+            if (e != cudaSuccess) return cuda_fail("copy_to_host", e);
+        }
+        return finish_blocking(d, "copy_to_host");
+    } catch (...) {
+        set_err("b200: copy_to_host raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+PtStatus copy_d2d(uint32_t device, void *dst, const void *src, size_t bytes) {
+    try {
+        B200_ENTER(device);
+        if (bytes == 0) return PT_STATUS_OK;
+        cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, d.stream);
+        return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("copy_device_to_device", e);
+    } catch (...) {
+        set_err("b200: copy_device_to_device raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+PtStatus synchronize(uint32_t device) {
+    try {
+        B200_ENTER(device);
+        return finish_blocking(d, "synchronize");
+    } catch (...) {
+        set_err("b200: synchronize raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+// ---- devices ------------------------------------------------------------------------------------------------
+
+uint32_t device_count() {
+    try {
+        return (uint32_t)visible_devices();
+    } catch (...) {
+        return 0;
+    }
+}
+
+PtStatus device_info(uint32_t device, PtDeviceInfo *out) {
+    try {
+        if (!out) return PT_STATUS_INVALID_ARGUMENT;
+        B200_ENTER(device);
+        cudaDeviceProp prop;
+        cudaError_t e = cudaGetDeviceProperties(&prop, (int)device);
+        if (e != cudaSuccess) return cuda_fail("device_info", e);
+        std::memset(out, 0, sizeof *out);
+        std::snprintf(out->name, sizeof out->name, "%.63s", prop.name);
+        out->kind = PT_KIND_CUDA;
+        size_t free_b = 0, total_b = 0;
+        if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+            out->total_memory = total_b;
+            // Cached blocks are reusable, so they count as free (plugins/cpu/src/lib.rs:208-209).
+            const size_t f = free_b + d.cached_bytes;
+            out->free_memory = f < total_b ? f : total_b;
+        } else {
+            (void)cudaGetLastError();
+            out->total_memory = out->free_memory = PT_MEMORY_UNKNOWN;
+        }
+        out->flags = 0;
+        return PT_STATUS_OK;
+    } catch (...) {
+        set_err("b200: device_info raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+const char *last_error() { return g_err; }
+
+// ---- execute ------------------------------------------------------------------------------------------------
+
+uint32_t supports_op(uint32_t code) {
+    switch (code) {
+        case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP:
+        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV:
+        case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS:
+        case PT_OP_COPY: case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_AXPY:
+            return 1;
+        default:
+            return 0;
+    }
+}
+
+// numel with overflow treated as "too big to be real".
+bool numel(const uint64_t *shape, uint32_t nd, uint64_t &n) {
+    n = 1;
+    for (uint32_t i = 0; i < nd; ++i) {
+        if (shape[i] != 0 && n > UINT64_MAX / shape[i]) return false;
+        n *= shape[i];
+    }
+    return true;
+}
+
+bool same_shape(const PtTensorDesc &a, const PtTensorDesc &b) {
+    if (a.ndim != b.ndim) return false;
+    for (uint32_t i = 0; i < a.ndim; ++i)
+        if (a.shape[i] != b.shape[i]) return false;
+    return true;
+}
+
+// Host-side coalescing, the reference's rule (plugins/cpu/src/ew.rs:22-43): drop size-1 dims, merge a
+// dim into its outer neighbour when that holds for every operand. Returns false if more than
+// MAX_DIMS dims remain.
+bool coalesce(const uint64_t *shape, uint32_t nd, const uint64_t *const *strides, int nops, EwProblem &p) {
+    p.nd = 0;
+    p.n = 1;
+    for (uint32_t i = 0; i < nd; ++i) {
+        const uint64_t s = shape[i];
+        p.n *= s;
+        if (s == 1) continue;
+        EwDim cur{};
+        cur.size = s;
+        for (int o = 0; o < nops; ++o) cur.stride[o] = strides[o][i];
+        if (p.nd > 0) {
+            EwDim &last = p.dim[p.nd - 1];
+            bool merge = true;
+            for (int o = 0; o < nops; ++o) merge = merge && last.stride[o] == cur.stride[o] * s;
+            if (merge) {
+                last.size *= s;
+                for (int o = 0; o < nops; ++o) last.stride[o] = cur.stride[o];
+                continue;
+            }
+        }
+        if (p.nd == MAX_DIMS) return false;
+        p.dim[p.nd++] = cur;
+    }
+    return true;
+}
+
+float bits_to_f32(int64_t v) {
+    const uint32_t b = (uint32_t)v;
+    float f;
+    std::memcpy(&f, &b, 4);
+    return f;
+}
+
+const char *op_name(uint32_t op) {
+    switch (op) {
+        case PT_OP_NEG: return "NEG"; case PT_OP_EXP: return "EXP"; case PT_OP_LOG: return "LOG";
+        case PT_OP_RELU: return "RELU"; case PT_OP_TANH: return "TANH"; case PT_OP_STEP: return "STEP";
+        case PT_OP_ADD: return "ADD"; case PT_OP_SUB: return "SUB"; case PT_OP_MUL: return "MUL"; case PT_OP_DIV: return "DIV";
+        case PT_OP_MATMUL: return "MATMUL"; case PT_OP_MATMUL_T: return "MATMUL_T"; case PT_OP_SUM_AXIS: return "SUM_AXIS";
+        case PT_OP_MAX_AXIS: return "MAX_AXIS"; case PT_OP_ARGMAX_AXIS: return "ARGMAX_AXIS"; case PT_OP_COPY: return "COPY";
+        case PT_OP_FILL: return "FILL"; case PT_OP_RAND_NORMAL: return "RAND_NORMAL"; case PT_OP_AXPY: return "AXPY";
+        default: return "?";
+    }
+}
+
+#define B200_INVALID(...)                   \
+    do {                                    \
+        set_err(__VA_ARGS__);               \
+        return PT_STATUS_INVALID_ARGUMENT;  \
+    } while (0)
+
+// Validation follows plugins/cpu/src/lib.rs:250-334 check for check.
+PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint32_t n_in,
+             const PtTensorDesc *outs, uint32_t n_out) {
+    if (n_out != 1) B200_INVALID("b200: op %u: %u outputs, expected 1", op, n_out);
+    uint32_t need;
+    switch (op) {
+        case PT_OP_FILL: case PT_OP_RAND_NORMAL: need = 0; break;
+        case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP: case PT_OP_COPY:
+        case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS: need = 1; break;
+        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_AXPY: need = 2; break;
+        default:
+            set_err("b200: op %u is not implemented", op);
+            return PT_STATUS_UNSUPPORTED;
+    }
+    if (n_in != need) B200_INVALID("b200: %s: %u inputs, expected %u", op_name(op), n_in, need);
+    // The only dtype is f32 (docs/plugin-abi.md:171-172); ARGMAX_AXIS alone writes i64.
+    for (uint32_t i = 0; i < n_in; ++i)
+        if (ins[i].dtype != PT_DTYPE_F32) {
+            set_err("b200: %s: input %u has dtype %u, only f32 is supported", op_name(op), i, ins[i].dtype);
+            return PT_STATUS_UNSUPPORTED;
+        }
+    if (outs[0].dtype != (op == PT_OP_ARGMAX_AXIS ? PT_DTYPE_I64 : PT_DTYPE_F32)) {
+        set_err("b200: %s: output dtype %u is not supported", op_name(op), outs[0].dtype);
+        return PT_STATUS_UNSUPPORTED;
+    }
+    const PtTensorDesc &o = outs[0];
+    uint64_t n;
+    if (!numel(o.shape, o.ndim, n)) B200_INVALID("b200: %s: output element count overflows", op_name(op));
+    float *out = (float *)o.data;
+    cudaError_t e = cudaSuccess;
+    switch (op) {
+        case PT_OP_FILL:
+            if (n) e = launch_fill(out, n, bits_to_f32(attrs.ints[0]), d.stream);
+            break;
+        case PT_OP_RAND_NORMAL:
+            if (n) e = launch_randn(out, n, (uint64_t)attrs.ints[0], d.stream);
+            break;
+        case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP: case PT_OP_COPY: {
+            uint64_t nx;
+            if (!numel(ins[0].shape, ins[0].ndim, nx) || nx != n)
+                B200_INVALID("b200: %s: input has %llu elements, output %llu", op_name(op), (unsigned long long)nx, (unsigned long long)n);
+            if (n == 0) break;
+            EwProblem p;
+            const uint64_t *st[1] = {ins[0].strides};
+            if (!coalesce(ins[0].shape, ins[0].ndim, st, 1, p)) {
+                set_err("b200: %s: more than %d non-mergeable dims", op_name(op), MAX_DIMS);
+                return PT_STATUS_UNSUPPORTED;
+            }
+            e = launch_unary(op, (const float *)ins[0].data, out, p, d.stream);
+            break;
+        }
+        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: {
+            if (!same_shape(ins[0], o) || !same_shape(ins[1], o)) B200_INVALID("b200: %s: operand shapes differ from the output's", op_name(op));
+            if (n == 0) break;
+            EwProblem p;
+            const uint64_t *st[2] = {ins[0].strides, ins[1].strides};
+            if (!coalesce(o.shape, o.ndim, st, 2, p)) {
+                set_err("b200: %s: more than %d non-mergeable dims", op_name(op), MAX_DIMS);
+                return PT_STATUS_UNSUPPORTED;
+            }
+            e = launch_binary(op, (const float *)ins[0].data, (const float *)ins[1].data, out, p, d.stream);
+            break;
+        }
+        case PT_OP_AXPY: {
+            uint64_t na, nb;
+            if (!numel(ins[0].shape, ins[0].ndim, na) || !numel(ins[1].shape, ins[1].ndim, nb) || na != n || nb != n)
+                B200_INVALID("b200: AXPY: operands have %llu and %llu elements, output %llu", (unsigned long long)na, (unsigned long long)nb, (unsigned long long)n);
+            if (n) e = launch_axpy((const float *)ins[0].data, (const float *)ins[1].data, out, bits_to_f32(attrs.ints[0]), n, d.stream);
+            break;
+        }
+        case PT_OP_MATMUL: case PT_OP_MATMUL_T: {
+            const PtTensorDesc &A = ins[0], &B = ins[1];
+            if (A.ndim != 2 || B.ndim != 2 || o.ndim != 2) B200_INVALID("b200: %s needs 2-D operands", op_name(op));
+            const int64_t flags = op == PT_OP_MATMUL_T ? attrs.ints[0] : 0;
+            const bool ta = flags & 1, tb = flags & 2;
+            const uint64_t m = ta ? A.shape[1] : A.shape[0], k = ta ? A.shape[0] : A.shape[1];
+            const uint64_t kb = tb ? B.shape[1] : B.shape[0], nn = tb ? B.shape[0] : B.shape[1];
+            if (k != kb || o.shape[0] != m || o.shape[1] != nn)
+                B200_INVALID("b200: %s: [%llu,%llu] x [%llu,%llu] does not give [%llu,%llu]", op_name(op), (unsigned long long)m, (unsigned long long)k,
+                             (unsigned long long)kb, (unsigned long long)nn, (unsigned long long)o.shape[0], (unsigned long long)o.shape[1]);
+            if (n == 0) break;
+            const uint64_t ars = ta ? A.strides[1] : A.strides[0], acs = ta ? A.strides[0] : A.strides[1];
+            const uint64_t brs = tb ? B.strides[1] : B.strides[0], bcs = tb ? B.strides[0] : B.strides[1];
+            e = launch_matmul((const float *)A.data, ars, acs, (const float *)B.data, brs, bcs, out, m, nn, k, d.stream);
+            break;
+        }
+        case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS: {
+            const PtTensorDesc &x = ins[0];
+            if (attrs.ints[0] < 0 || (uint64_t)attrs.ints[0] >= x.ndim)
+                B200_INVALID("b200: %s: axis %lld out of range for %u dims", op_name(op), (long long)attrs.ints[0], x.ndim);
+            const uint32_t axis = (uint32_t)attrs.ints[0];
+            uint64_t outer, inner;
+            const uint64_t len = x.shape[axis];
+            if (!numel(x.shape, axis, outer) || !numel(x.shape + axis + 1, x.ndim - axis - 1, inner) || outer * inner != n)
+                B200_INVALID("b200: %s: output has %llu elements, expected %llu", op_name(op), (unsigned long long)n, (unsigned long long)(outer * inner));
+            if (n == 0) break;
+            const ReduceKind kind = op == PT_OP_SUM_AXIS ? REDUCE_SUM : op == PT_OP_MAX_AXIS ? REDUCE_MAX : REDUCE_ARGMAX;
+            if (kind != REDUCE_SUM && len == 0) B200_INVALID("b200: %s over an empty axis has no value", op_name(op));
+            // Two-pass reductions keep their per-block partials in a scratch block from the cache; it
+            // goes back right after the launches, the stream orders any reuse behind them.
+            void *scratch = nullptr;
+            const size_t sb = reduce_scratch_bytes(kind, outer, len, inner, (int)device);
+            if (sb) {
+                PtStatus st = alloc_locked(d, sb, &scratch);
+                if (st != PT_STATUS_OK) return st;
+            }
+            e = launch_reduce(kind, (const float *)x.data, outer, len, inner, o.data, scratch, (int)device, d.stream);
+            if (scratch) free_locked(d, scratch);
+            break;
+        }
+        default:
+            return PT_STATUS_UNSUPPORTED;
+    }
+    if (e != cudaSuccess) return cuda_fail(op_name(op), e);
+    return PT_STATUS_OK;
+}
+
+PtStatus execute(uint32_t device, uint32_t op, const PtOpAttrs *attrs, const PtTensorDesc *ins, uint32_t n_in,
+                 const PtTensorDesc *outs, uint32_t n_out) {
+    try {
+        PtOpAttrs a{};
+        if (attrs) a = *attrs;
+        B200_ENTER(device);
+        return run(d, device, op, a, ins, n_in, outs, n_out);
+    } catch (...) {
+        set_err("b200: op %u raised an exception", op);
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+const PtPluginVTable VTABLE = {
+    PT_ABI_VERSION, PT_VTABLE_SIZE, 1, "b200",
+    device_count, device_info, alloc_buf, free_buf, copy_from_host, copy_to_host, copy_d2d,
+    supports_op, execute, synchronize, last_error,
+};
+
+}  // namespace
+
+int sm_count(int device) {
+    if (device < 0) (void)cudaGetDevice(&device);
+    if (device >= 0 && device < MAX_DEVICES && g_dev[device].sms) return g_dev[device].sms;
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) n = 148;
+    return n;
+}
+
+}  // namespace b200
+
+#define B200_EXPORT __attribute__((visibility("default")))
+
+extern "C" {
+
+B200_EXPORT const PtPluginVTable *pytorches_plugin_entry(void) { return &b200::VTABLE; }
+
+B200_EXPORT void *pytorches_b200_stream(uint32_t device) {
+    try {
+        if (!b200::valid_device(device)) return nullptr;
+        b200::DeviceState &d = b200::g_dev[device];
+        std::lock_guard<std::mutex> lock(d.mu);
+        if (b200::ensure_device(device) != cudaSuccess) return nullptr;
+        return (void *)d.stream;
+    } catch (...) {
+        return nullptr;
+    }
+}
+
+B200_EXPORT uint64_t pytorches_b200_kernel_launches(void) { return b200::g_kernel_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

@@ -1,0 +1,361 @@
+// Reduction kernels of the B200 plugin: SUM_AXIS (in place of plugins/cpu/src/reduce.rs) and the
+// appended MAX_AXIS / ARGMAX_AXIS, over the middle axis of a contiguous (outer, len, inner) tensor.
+//
+// SUM reproduces the reference's association order, so its results carry the reference's bits:
+//   * inner == 1 (reduce.rs:110-131): a row is cut into 65536-element blocks. Within a block element i
+//     is accumulated, in order, into slot i mod 32; the 32 slots are combined pairwise at distances
+//     8, 16, 4, 2, 1; the last (block length mod 32) elements are then added one by one; block sums
+//     are added in block order starting from 0.0. A warp is exactly that machine: lane j owns slot j
+//     (its loads, x[32k + j], are perfectly coalesced), and the slot combine is a shuffle tree with
+//     the same distances. Pass 1 gives one warp to every (row, block); pass 2, only needed when a row
+//     has more than one block, adds a row's block sums in order. No atomics, so reruns are identical.
+//   * inner > 1 (reduce.rs:132-145): every output column adds its len inputs in order from 0.0; one
+//     thread per column, loads of neighbouring threads coalesce.
+// MAX / ARGMAX have no reference implementation; they follow torch CPU (NaN wins, first index on
+// ties). max is order-independent, so these use float4 loads and a two-pass (value, index) combine.
+//
+// All kernels are pure HBM streaming: every load of a thread's batch is issued before the first use.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr uint64_t SUM_BLOCK = 1ull << 16;  // reduce.rs:10
+constexpr int SUM_WARPS = 2;                // warps per CTA in pass 1
+constexpr int SUM_UNROLL = 16;              // loads in flight per lane
+
+__device__ __forceinline__ float ldf(const float *p) { return __ldcs(p); }
+__device__ __forceinline__ float4 ldf4(const float *p) { return __ldcs(reinterpret_cast<const float4 *>(p)); }
+
+// Sum of m <= 65536 contiguous elements in the reference's order (reduce.rs:36-61). Whole warp calls;
+// the result is valid in lane 0.
+__device__ __forceinline__ float warp_block_sum(const float *__restrict__ p, uint32_t m, int lane) {
+    const uint32_t m32 = m & ~31u;
+    float s = 0.0f;
+    uint32_t k = lane;
+    for (; k + 32 * (SUM_UNROLL - 1) < m32; k += 32 * SUM_UNROLL) {
+        float v[SUM_UNROLL];
+#pragma unroll
+        for (int u = 0; u < SUM_UNROLL; ++u) v[u] = ldf(p + k + 32 * u);
+#pragma unroll
+        for (int u = 0; u < SUM_UNROLL; ++u) s = __fadd_rn(s, v[u]);
+    }
+    for (; k < m32; k += 32) s = __fadd_rn(s, ldf(p + k));
+    // (a0+a1)+(a2+a3), then high half onto low half, then lanes (0+2),(1+3), then those two.
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 8));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 16));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 4));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 2));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 1));
+    if (lane == 0)
+        for (uint32_t i = m32; i < m; ++i) s = __fadd_rn(s, p[i]);
+    return s;
+}
+
+// Pass 1, inner == 1: warp t handles block (t mod blocks) of row (t div blocks). With one block per
+// row the row's result is written directly as 0.0 + block sum (the reference's combine loop).
+__global__ void __launch_bounds__(32 * SUM_WARPS) sum_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
+                                                                  uint64_t blocks, float *__restrict__ dst) {
+    const uint64_t t = (uint64_t)blockIdx.x * SUM_WARPS + (threadIdx.x >> 5);
+    if (t >= tasks) return;
+    const int lane = threadIdx.x & 31;
+    const uint64_t row = t / blocks, b = t - row * blocks;
+    const uint64_t lo = b * SUM_BLOCK;
+    const uint32_t m = (uint32_t)(len - lo < SUM_BLOCK ? len - lo : SUM_BLOCK);
+    const float s = warp_block_sum(x + row * len + lo, m, lane);
+    if (lane == 0) dst[t] = blocks == 1 ? __fadd_rn(0.0f, s) : s;
+}
+
+// Rows shorter than 32 elements never fill a slot: the reference adds them one by one to 0.0.
+__global__ void __launch_bounds__(256) sum_short_rows_kernel(const float *__restrict__ x, uint64_t outer, uint32_t len,
+                                                             float *__restrict__ out) {
+    const uint64_t r = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (r >= outer) return;
+    const float *p = x + r * len;
+    float s = 0.0f;
+    for (uint32_t i = 0; i < len; ++i) s = __fadd_rn(s, p[i]);
+    out[r] = __fadd_rn(0.0f, s);
+}
+
+// Pass 2, inner == 1: out[row] = ((0.0 + p[0]) + p[1]) + ... in block order. One warp per row stages
+// the partials through shared memory with coalesced loads; lane 0 does the ordered chain.
+constexpr int COMBINE_STAGE = 2048;
+__global__ void __launch_bounds__(32) sum_combine_kernel(const float *__restrict__ partial, uint64_t blocks, float *__restrict__ out) {
+    __shared__ float stage[COMBINE_STAGE];
+    const uint64_t row = blockIdx.x;
+    const float *p = partial + row * blocks;
+    float s = 0.0f;
+    for (uint64_t base = 0; base < blocks; base += COMBINE_STAGE) {
+        const uint32_t m = (uint32_t)(blocks - base < COMBINE_STAGE ? blocks - base : COMBINE_STAGE);
+        for (uint32_t i = threadIdx.x; i < m; i += 32) stage[i] = p[base + i];
+        __syncwarp();
+        if (threadIdx.x == 0)
+            for (uint32_t i = 0; i < m; ++i) s = __fadd_rn(s, stage[i]);
+        __syncwarp();
+    }
+    if (threadIdx.x == 0) out[row] = s;
+}
+
+// inner > 1: thread per output column, rows j added in order from 0.0.
+constexpr int COL_UNROLL = 8;
+__global__ void __launch_bounds__(256) sum_cols_kernel(const float *__restrict__ x, uint64_t total, uint64_t len, uint64_t inner,
+                                                       float *__restrict__ out) {
+    const uint64_t t = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (t >= total) return;
+    const uint64_t o = t / inner, i = t - o * inner;
+    const float *p = x + o * len * inner + i;
+    float s = 0.0f;
+    uint64_t j = 0;
+    for (; j + COL_UNROLL <= len; j += COL_UNROLL) {
+        float v[COL_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COL_UNROLL; ++u) v[u] = ldf(p + (j + u) * inner);
+#pragma unroll
+        for (int u = 0; u < COL_UNROLL; ++u) s = __fadd_rn(s, v[u]);
+    }
+    for (; j < len; ++j) s = __fadd_rn(s, ldf(p + j * inner));
+    out[t] = s;
+}
+
+// ---- max / argmax ---------------------------------------------------------------------------------------
+
+// Should candidate (v, i) replace the current best (bv, bi)? NaN beats every number; among equals
+// (or among NaNs) the lower index wins.
+__device__ __forceinline__ bool vi_better(float v, uint64_t i, float bv, uint64_t bi) {
+    const bool vn = v != v, bn = bv != bv;
+    if (vn || bn) return vn && (!bn || i < bi);
+    return v > bv || (v == bv && i < bi);
+}
+
+// Scanning in increasing index order: strictly greater replaces; a NaN replaces a non-NaN.
+__device__ __forceinline__ void scan_step(float v, uint64_t i, float &bv, uint64_t &bi) {
+    if (v > bv || (v != v && bv == bv)) {
+        bv = v;
+        bi = i;
+    }
+}
+
+constexpr int MAX_CTA = 256;
+constexpr int MAX_UNROLL = 4;
+
+// inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
+// threads share one task (32: a warp per task, 256: the CTA). VEC 4 requires every task start to be
+// 16-byte aligned (the host guarantees it). Writes the value and/or the index WITHIN THE ROW.
+template <int TPT, int VEC, bool ARG>
+__global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
+                                                           uint64_t segs, uint64_t seg_len, float *__restrict__ out_v,
+                                                           int64_t *__restrict__ out_i) {
+    constexpr int PER_CTA = MAX_CTA / TPT;
+    const uint64_t t = (uint64_t)blockIdx.x * PER_CTA + threadIdx.x / TPT;
+    const int lane = threadIdx.x % TPT;
+    const bool live = t < tasks;
+    // Every thread starts from (-inf, first index it will look at), so a slice of nothing but -inf
+    // still reports its first position; a thread with nothing to look at holds (-inf, ~0).
+    float bv = __int_as_float(0xff800000);
+    uint64_t bi = ~0ull;
+    if (live) {
+        const uint64_t row = t / segs, seg = t - row * segs;
+        const uint64_t lo = seg * seg_len;
+        const uint64_t hi = lo + seg_len < len ? lo + seg_len : len;
+        const float *p = x + row * len;
+        if constexpr (VEC == 4) {
+            const uint64_t vend = lo + ((hi - lo) & ~3ull);
+            uint64_t i = lo + (uint64_t)lane * 4;
+            if (i < vend) bi = i;
+            else if (lane == 0 && vend < hi) bi = vend;
+            for (; i + (uint64_t)(MAX_UNROLL - 1) * TPT * 4 < vend; i += (uint64_t)MAX_UNROLL * TPT * 4) {
+                float4 v[MAX_UNROLL];
+#pragma unroll
+                for (int u = 0; u < MAX_UNROLL; ++u) v[u] = ldf4(p + i + (uint64_t)u * TPT * 4);
+#pragma unroll
+                for (int u = 0; u < MAX_UNROLL; ++u) {
+                    const uint64_t j = i + (uint64_t)u * TPT * 4;
+                    scan_step(v[u].x, j, bv, bi);
+                    scan_step(v[u].y, j + 1, bv, bi);
+                    scan_step(v[u].z, j + 2, bv, bi);
+                    scan_step(v[u].w, j + 3, bv, bi);
+                }
+            }
+            for (; i < vend; i += (uint64_t)TPT * 4) {
+                const float4 v = ldf4(p + i);
+                scan_step(v.x, i, bv, bi);
+                scan_step(v.y, i + 1, bv, bi);
+                scan_step(v.z, i + 2, bv, bi);
+                scan_step(v.w, i + 3, bv, bi);
+            }
+            if (lane == 0)
+                for (uint64_t j = vend; j < hi; ++j)
+                    if (vi_better(p[j], j, bv, bi)) { bv = p[j]; bi = j; }
+        } else {
+            if (lo + lane < hi) bi = lo + lane;
+            for (uint64_t i = lo + lane; i < hi; i += TPT) scan_step(ldf(p + i), i, bv, bi);
+        }
+    }
+    // (-inf, ~0) loses every comparison against a real element: equal values resolve to the lower index.
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const uint64_t oi = __shfl_xor_sync(0xffffffffu, bi, d);
+        if (vi_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if constexpr (TPT > 32) {
+        __shared__ float sv[TPT / 32];
+        __shared__ uint64_t si[TPT / 32];
+        if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            bv = threadIdx.x < TPT / 32 ? sv[threadIdx.x] : __int_as_float(0xff800000);
+            bi = threadIdx.x < TPT / 32 ? si[threadIdx.x] : ~0ull;
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+                const uint64_t oi = __shfl_xor_sync(0xffffffffu, bi, d);
+                if (vi_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+        }
+    }
+    if (live && lane == 0) {
+        if (out_v) out_v[t] = bv;
+        if (ARG && out_i) out_i[t] = (int64_t)bi;
+    }
+}
+
+// Pass 2 for rows split into several segments: thread per row scans its segment results in order.
+template <bool ARG>
+__global__ void __launch_bounds__(256) max_combine_kernel(const float *__restrict__ pv, const int64_t *__restrict__ pi, uint64_t outer,
+                                                          uint64_t segs, float *__restrict__ out_v, int64_t *__restrict__ out_i) {
+    const uint64_t r = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (r >= outer) return;
+    float bv = pv[r * segs];
+    uint64_t bs = 0;
+    for (uint64_t s = 1; s < segs; ++s) scan_step(pv[r * segs + s], s, bv, bs);
+    if (ARG) out_i[r] = pi[r * segs + bs];
+    else out_v[r] = bv;
+}
+
+// inner > 1: thread per output column scans rows j in order.
+template <bool ARG>
+__global__ void __launch_bounds__(256) max_cols_kernel(const float *__restrict__ x, uint64_t total, uint64_t len, uint64_t inner,
+                                                       float *__restrict__ out_v, int64_t *__restrict__ out_i) {
+    const uint64_t t = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (t >= total) return;
+    const uint64_t o = t / inner, i = t - o * inner;
+    const float *p = x + o * len * inner + i;
+    float bv = ldf(p);
+    uint64_t bi = 0;
+    uint64_t j = 1;
+    for (; j + COL_UNROLL <= len; j += COL_UNROLL) {
+        float v[COL_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COL_UNROLL; ++u) v[u] = ldf(p + (j + u) * inner);
+#pragma unroll
+        for (int u = 0; u < COL_UNROLL; ++u) scan_step(v[u], j + u, bv, bi);
+    }
+    for (; j < len; ++j) scan_step(ldf(p + j * inner), j, bv, bi);
+    if (ARG) out_i[t] = (int64_t)bi;
+    else out_v[t] = bv;
+}
+
+// ---- host-side planning ------------------------------------------------------------------------------------
+
+struct MaxPlan {
+    int tpt;           // threads per task: 32 or 256
+    int vec;           // 1 or 4
+    uint64_t segs;     // segments per row
+    uint64_t seg_len;  // elements per segment (multiple of 4)
+};
+
+MaxPlan plan_max(uint64_t outer, uint64_t len, int sms) {
+    MaxPlan m;
+    m.vec = (len % 4 == 0 || outer == 1) ? 4 : 1;
+    if (len <= 16384) {
+        m.tpt = 32;
+        m.segs = 1;
+        m.seg_len = (len + 3) & ~3ull;
+        return m;
+    }
+    m.tpt = 256;
+    const uint64_t target = (uint64_t)sms * 16;  // CTAs wanted in flight
+    uint64_t segs = (target + outer - 1) / outer;
+    const uint64_t max_segs = (len + 16383) / 16384;
+    if (segs > max_segs) segs = max_segs;
+    if (segs < 1) segs = 1;
+    uint64_t seg_len = (len + segs - 1) / segs;
+    seg_len = (seg_len + 1023) & ~1023ull;
+    m.seg_len = seg_len;
+    m.segs = (len + seg_len - 1) / seg_len;
+    return m;
+}
+
+}  // namespace
+
+size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device) {
+    if (inner != 1 || outer == 0 || len == 0) return 0;
+    if (kind == REDUCE_SUM) {
+        const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK;
+        return blocks > 1 ? outer * blocks * sizeof(float) : 0;
+    }
+    const MaxPlan m = plan_max(outer, len, sm_count(device));
+    if (m.segs == 1) return 0;
+    const uint64_t tasks = outer * m.segs;
+    // values, then (16-byte aligned) indices
+    return ((tasks * 4 + 15) & ~15ull) + (kind == REDUCE_ARGMAX ? tasks * 8 : 0);
+}
+
+cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, void *out, void *scratch,
+                          int device, cudaStream_t s) {
+    const uint64_t total = outer * inner;
+    if (total == 0) return cudaSuccess;
+    if (kind == REDUCE_SUM) {
+        float *o = (float *)out;
+        if (len == 0) return launch_fill(o, total, 0.0f, s);  // reduce.rs:106-109
+        if (inner == 1) {
+            if (len < 32) {
+                B200_LAUNCH(sum_short_rows_kernel, (unsigned)((outer + 255) / 256), 256, 0, s, x, outer, (uint32_t)len, o);
+                return cudaGetLastError();
+            }
+            const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK, tasks = outer * blocks;
+            float *dst = blocks == 1 ? o : (float *)scratch;
+            B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
+            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, 32, 0, s, (const float *)scratch, blocks, o);
+            return cudaGetLastError();
+        }
+        B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
+        return cudaGetLastError();
+    }
+    const bool arg = kind == REDUCE_ARGMAX;
+    float *ov = arg ? nullptr : (float *)out;
+    int64_t *oi = arg ? (int64_t *)out : nullptr;
+    if (inner != 1) {
+        if (arg) B200_LAUNCH(max_cols_kernel<true>, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi);
+        else B200_LAUNCH(max_cols_kernel<false>, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi);
+        return cudaGetLastError();
+    }
+    const MaxPlan m = plan_max(outer, len, sm_count(device));
+    const uint64_t tasks = outer * m.segs;
+    float *pv = ov;
+    int64_t *pi = oi;
+    if (m.segs > 1) {
+        pv = (float *)scratch;
+        pi = arg ? (int64_t *)((char *)scratch + ((tasks * 4 + 15) & ~15ull)) : nullptr;
+    }
+    const unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
+#define B200_MAX_CASE(TPT, VEC)                                                                                          \
+    if (m.tpt == TPT && m.vec == VEC) {                                                                                  \
+        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi); \
+        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi);    \
+    }
+    B200_MAX_CASE(32, 1)
+    B200_MAX_CASE(32, 4)
+    B200_MAX_CASE(256, 1)
+    B200_MAX_CASE(256, 4)
+#undef B200_MAX_CASE
+    if (m.segs > 1) {
+        if (arg) B200_LAUNCH(max_combine_kernel<true>, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi);
+        else B200_LAUNCH(max_combine_kernel<false>, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace b200
