@@ -78,6 +78,16 @@ enum {
      * axis is PT_STATUS_INVALID_ARGUMENT (there is no identity to return). */
     PT_OP_MAX_AXIS = 203,
     PT_OP_ARGMAX_AXIS = 204,
+    /* appended, for reductions sharded over several devices (one pass over the data, then a combine
+     * of per-device results; no counterpart in the reference):
+     * MAX_ARGMAX_AXIS: one input; TWO outputs over the same reduced shape, outputs[0] the f32 maxima
+     *   (as MAX_AXIS) and outputs[1] the i64 positions (as ARGMAX_AXIS) plus ints[1], the position of
+     *   this shard's first row in the unsharded axis. It is the only op with two outputs.
+     * ARGMAX_COMBINE: inputs[0] f32 [G, ...] candidate maxima and inputs[1] i64 [G, ...] their
+     *   positions, one row per shard; output i64 [...]: per column the position of the best
+     *   candidate (NaN wins, then the larger value, then the lower position). */
+    PT_OP_MAX_ARGMAX_AXIS = 205,
+    PT_OP_ARGMAX_COMBINE = 206,
 
     PT_OP_COPY = 300, /* materialise a strided / broadcast input contiguously */
 

@@ -130,7 +130,7 @@ uint32_t supports_op(uint32_t code) {
         case OP_NEG: case OP_EXP: case OP_LOG: case OP_RELU: case OP_TANH: case OP_STEP:
         case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV:
         case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY: case OP_SUM_AXIS: case OP_COPY: case OP_FILL: case OP_RAND_NORMAL:
-        case OP_MAX_AXIS: case OP_ARGMAX_AXIS:
+        case OP_MAX_AXIS: case OP_ARGMAX_AXIS: case OP_MAX_ARGMAX_AXIS: case OP_ARGMAX_COMBINE:
             return 1;
         default: return 0;
     }
@@ -147,6 +147,32 @@ bool same_shape(const PtTensorDesc &a, const PtTensorDesc &b) {
     for (uint32_t d = 0; d < a.ndim; ++d)
         if (a.shape[d] != b.shape[d]) return false;
     return true;
+}
+
+// The two appended ops for sharded argmax (not in the reference).
+PtStatus run_sharded_argmax(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint32_t n_in, const PtTensorDesc *outs, uint32_t n_out) {
+    if (op == OP_MAX_ARGMAX_AXIS) {
+        if (n_in != 1 || n_out != 2) return PT_STATUS_INVALID_ARGUMENT;
+        const PtTensorDesc &x = ins[0];
+        if (x.dtype != PT_DTYPE_F32 || outs[0].dtype != PT_DTYPE_F32 || outs[1].dtype != PT_DTYPE_I64) return PT_STATUS_UNSUPPORTED;
+        if (attrs.ints[0] < 0 || (uint64_t)attrs.ints[0] >= x.ndim) return PT_STATUS_INVALID_ARGUMENT;
+        const size_t axis = (size_t)attrs.ints[0];
+        const size_t outer = numel(x.shape, axis), len = (size_t)x.shape[axis], inner = numel(x.shape + axis + 1, x.ndim - axis - 1);
+        if (outer * inner != numel(outs[0].shape, outs[0].ndim) || outer * inner != numel(outs[1].shape, outs[1].ndim)) return PT_STATUS_INVALID_ARGUMENT;
+        if (outer * inner == 0) return PT_STATUS_OK;
+        if (len == 0) return PT_STATUS_INVALID_ARGUMENT;
+        max_axis((const float *)x.data, outer, len, inner, (float *)outs[0].data, (int64_t *)outs[1].data, attrs.ints[1]);
+        return PT_STATUS_OK;
+    }
+    if (n_in != 2 || n_out != 1) return PT_STATUS_INVALID_ARGUMENT;
+    if (ins[0].dtype != PT_DTYPE_F32 || ins[1].dtype != PT_DTYPE_I64 || outs[0].dtype != PT_DTYPE_I64) return PT_STATUS_UNSUPPORTED;
+    if (ins[0].ndim < 1 || !same_shape(ins[0], ins[1])) return PT_STATUS_INVALID_ARGUMENT;
+    const size_t g = (size_t)ins[0].shape[0], m = numel(ins[0].shape + 1, ins[0].ndim - 1);
+    if (m != numel(outs[0].shape, outs[0].ndim)) return PT_STATUS_INVALID_ARGUMENT;
+    if (m == 0) return PT_STATUS_OK;
+    if (g == 0) return PT_STATUS_INVALID_ARGUMENT;
+    argmax_combine((const float *)ins[0].data, (const int64_t *)ins[1].data, g, m, (int64_t *)outs[0].data);
+    return PT_STATUS_OK;
 }
 
 PtStatus run(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint32_t n_in, const PtTensorDesc *outs, uint32_t n_out) {
@@ -227,6 +253,11 @@ PtStatus execute(uint32_t, uint32_t op, const PtOpAttrs *attrs, const PtTensorDe
     try {  // lib.rs:345-352: nothing may unwind across the boundary
         PtOpAttrs a{};
         if (attrs) a = *attrs;
+        if (op == OP_MAX_ARGMAX_AXIS || op == OP_ARGMAX_COMBINE) {
+            PtStatus s = run_sharded_argmax(op, a, ins, n_in, outs, n_out);
+            if (s != PT_STATUS_OK) set_err("cpuref: op %llu failed with status %llu", op, (unsigned long long)s);
+            return s;
+        }
         // The only dtype is f32 (docs/plugin-abi.md:171-172), except ARGMAX_AXIS's i64 output.
         for (uint32_t i = 0; i < n_in; ++i)
             if (ins[i].dtype != PT_DTYPE_F32) return PT_STATUS_UNSUPPORTED;

@@ -24,6 +24,7 @@ enum : uint32_t {
     OP_NEG = 1, OP_EXP = 2, OP_LOG = 3, OP_RELU = 4, OP_TANH = 5, OP_STEP = 6,
     OP_ADD = 100, OP_SUB = 101, OP_MUL = 102, OP_DIV = 103,
     OP_MATMUL = 200, OP_SUM_AXIS = 201, OP_MATMUL_T = 202, OP_MAX_AXIS = 203, OP_ARGMAX_AXIS = 204,
+    OP_MAX_ARGMAX_AXIS = 205, OP_ARGMAX_COMBINE = 206,
     OP_COPY = 300, OP_FILL = 400, OP_RAND_NORMAL = 401, OP_AXPY = 500,
 };
 
@@ -371,25 +372,75 @@ inline void sum_axis(const float *x, size_t outer, size_t n, size_t inner, float
 
 // ---- max / argmax over an axis: NOT in the reference ----------------------------------------------
 // torch CPU semantics: a NaN wins (first NaN position for argmax); ties keep the lowest index.
-inline void max_axis(const float *x, size_t outer, size_t n, size_t inner, float *out_val, int64_t *out_idx) {
+inline void max_scan(const float *p, size_t stride, size_t lo, size_t hi, float &best, int64_t &bi) {
+    best = p[lo * stride];
+    bi = (int64_t)lo;
+    for (size_t j = lo + 1; j < hi && !(best != best); ++j) {
+        const float v = p[j * stride];
+        if (v > best || v != v) {
+            best = v;
+            bi = (int64_t)j;
+        }
+    }
+}
+
+inline void max_axis(const float *x, size_t outer, size_t n, size_t inner, float *out_val, int64_t *out_idx, int64_t idx_offset = 0) {
     const size_t total = outer * inner;
-    Pool::get().for_chunks(total, 256, [&](size_t lo, size_t hi) {
-        for (size_t t = lo; t < hi; ++t) {
-            size_t o = t / inner, i = t % inner;
-            const float *p = x + o * n * inner + i;
-            float best = p[0];
-            int64_t bi = 0;
-            for (size_t j = 1; j < n && !(best != best); ++j) {
-                float v = p[j * inner];
+    if (inner == 1 && n > BLOCK) {
+        // Long rows: scan BLOCK-sized pieces in parallel, then keep the first best piece. The result
+        // does not depend on the split, so this is the same function as the plain scan below.
+        const size_t blocks = (n + BLOCK - 1) / BLOCK;
+        std::vector<float> pv(outer * blocks);
+        std::vector<int64_t> pi(outer * blocks);
+        Pool::get().run_tasks(outer * blocks, [&](size_t t) {
+            const size_t row = t / blocks, b = t % blocks;
+            max_scan(x + row * n, 1, b * BLOCK, std::min((b + 1) * BLOCK, n), pv[t], pi[t]);
+        });
+        for (size_t row = 0; row < outer; ++row) {
+            float best = pv[row * blocks];
+            int64_t bi = pi[row * blocks];
+            for (size_t b = 1; b < blocks && !(best != best); ++b) {
+                const float v = pv[row * blocks + b];
                 if (v > best || v != v) {
                     best = v;
-                    bi = (int64_t)j;
+                    bi = pi[row * blocks + b];
                 }
             }
+            if (out_val) out_val[row] = best;
+            if (out_idx) out_idx[row] = bi + idx_offset;
+        }
+        return;
+    }
+    Pool::get().for_chunks(total, 256, [&](size_t lo, size_t hi) {
+        for (size_t t = lo; t < hi; ++t) {
+            const size_t o = t / inner, i = t % inner;
+            float best;
+            int64_t bi;
+            max_scan(x + o * n * inner + i, inner, 0, n, best, bi);
             if (out_val) out_val[t] = best;
-            if (out_idx) out_idx[t] = bi;
+            if (out_idx) out_idx[t] = bi + idx_offset;
         }
     });
+}
+
+// Picks, per column, the best of G candidates (value, position): NaN wins, then the larger value,
+// then the lower position. Combines per-shard results of a sharded argmax. NOT in the reference.
+inline void argmax_combine(const float *vals, const int64_t *idx, size_t g, size_t m, int64_t *out) {
+    for (size_t j = 0; j < m; ++j) {
+        float bv = vals[j];
+        int64_t bi = idx[j];
+        for (size_t r = 1; r < g; ++r) {
+            const float v = vals[r * m + j];
+            const int64_t i = idx[r * m + j];
+            const bool vn = v != v, bn = bv != bv;
+            const bool better = (vn || bn) ? (vn && (!bn || i < bi)) : (v > bv || (v == bv && i < bi));
+            if (better) {
+                bv = v;
+                bi = i;
+            }
+        }
+        out[j] = bi;
+    }
 }
 
 // ---- matmul: required by the ABI, outside the measured path ------------------------------------------

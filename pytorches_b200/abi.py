@@ -26,12 +26,13 @@ MEMORY_UNKNOWN = 2**64 - 1
 
 
 class op:
-    """Op codes (crates/plugin-abi/src/lib.rs:67-115); 203/204 are appended codes."""
+    """Op codes (crates/plugin-abi/src/lib.rs:67-115); 203-206 are appended codes."""
 
     NEG, EXP, LOG, RELU, TANH, STEP = 1, 2, 3, 4, 5, 6
     ADD, SUB, MUL, DIV = 100, 101, 102, 103
     MATMUL, SUM_AXIS, MATMUL_T = 200, 201, 202
     MAX_AXIS, ARGMAX_AXIS = 203, 204
+    MAX_ARGMAX_AXIS, ARGMAX_COMBINE = 205, 206  # appended, for sharded reductions
     COPY = 300
     FILL, RAND_NORMAL = 400, 401
     AXPY = 500

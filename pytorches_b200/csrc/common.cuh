@@ -67,10 +67,14 @@ cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const floa
 // Reductions over the middle axis of a contiguous (outer, len, inner) tensor. `scratch` must hold
 // reduce_scratch_bytes(...) bytes (0 means none is needed); it is global memory the kernels use for
 // per-block partial results between their two passes.
-enum ReduceKind : int { REDUCE_SUM = 0, REDUCE_MAX = 1, REDUCE_ARGMAX = 2 };
+// SUM and MAX write f32 values to out_v, ARGMAX i64 positions to out_i, MAX_ARGMAX both; positions
+// get idx_offset added (the shard's first row when the axis is split over devices).
+enum ReduceKind : int { REDUCE_SUM = 0, REDUCE_MAX = 1, REDUCE_ARGMAX = 2, REDUCE_MAX_ARGMAX = 3 };
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
-cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, void *out,
-                          void *scratch, int device, cudaStream_t s);
+cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v,
+                          int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s);
+// Per column of [g, m] candidates (value, position), the position of the best one.
+cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s);
 
 }  // namespace b200
 

@@ -32,13 +32,61 @@ enum : uint32_t {
 // ---- per-element functors ------------------------------------------------------------------------
 // Unary semantics follow plugins/cpu/src/ew.rs:96-106 (RELU is max(v, 0) with NaN -> 0; STEP is v > 0).
 template <uint32_t OP> struct UnaryFn;
-template <> struct UnaryFn<OP_NEG> { __device__ __forceinline__ static float f(float v) { return -v; } };
-template <> struct UnaryFn<OP_RELU> { __device__ __forceinline__ static float f(float v) { return v > 0.0f ? v : 0.0f; } };
-template <> struct UnaryFn<OP_STEP> { __device__ __forceinline__ static float f(float v) { return v > 0.0f ? 1.0f : 0.0f; } };
-template <> struct UnaryFn<OP_EXP> { __device__ __forceinline__ static float f(float v) { return exp_ref(v); } };
-template <> struct UnaryFn<OP_LOG> { __device__ __forceinline__ static float f(float v) { return log_ref(v); } };
-template <> struct UnaryFn<OP_TANH> { __device__ __forceinline__ static float f(float v) { return tanh_ref(v); } };
-template <> struct UnaryFn<OP_COPY> { __device__ __forceinline__ static float f(float v) { return v; } };
+template <> struct UnaryFn<OP_NEG> { static constexpr bool SPLIT = false; __device__ __forceinline__ static float f(float v) { return -v; } };
+template <> struct UnaryFn<OP_RELU> { static constexpr bool SPLIT = false; __device__ __forceinline__ static float f(float v) { return v > 0.0f ? v : 0.0f; } };
+template <> struct UnaryFn<OP_STEP> { static constexpr bool SPLIT = false; __device__ __forceinline__ static float f(float v) { return v > 0.0f ? 1.0f : 0.0f; } };
+template <> struct UnaryFn<OP_COPY> { static constexpr bool SPLIT = false; __device__ __forceinline__ static float f(float v) { return v; } };
+// EXP/LOG/TANH: `f` is the reference's vector polynomial. `libm` stands in for the C library call the
+// reference makes on the elements its 8-wide vector loop does not cover (plugins/cpu/src/ew.rs:114-138):
+// evaluated in double and rounded once, it is correctly rounded in all but vanishingly rare cases and
+// so within an ulp or two of any good libm.
+template <> struct UnaryFn<OP_EXP> {
+    static constexpr bool SPLIT = true;
+    __device__ __forceinline__ static float f(float v) { return exp_ref(v); }
+    __device__ __noinline__ static float libm(float v) { return (float)exp((double)v); }
+};
+template <> struct UnaryFn<OP_LOG> {
+    static constexpr bool SPLIT = true;
+    __device__ __forceinline__ static float f(float v) { return log_ref(v); }
+    __device__ __noinline__ static float libm(float v) { return (float)log((double)v); }
+};
+template <> struct UnaryFn<OP_TANH> {
+    static constexpr bool SPLIT = true;
+    __device__ __forceinline__ static float f(float v) { return tanh_ref(v); }
+    __device__ __noinline__ static float libm(float v) { return (float)tanh((double)v); }
+};
+
+// Which elements of a unary op the reference computes with libm instead of its vector polynomial.
+// The reference cuts the output into chunks of 65536 elements (the whole tensor below 32768,
+// ew.rs:13-15,160), walks each chunk as runs of the innermost dim (ew.rs:46-87), and per run:
+//   inner stride 1: polynomial on the first len/8*8 elements of the run, libm on the rest;
+//   inner stride 0: one value, computed alone, hence by libm (ew.rs:168-172);
+//   other strides:  the run is gathered 256 elements at a time and each piece is split the same way.
+struct LibmSplit {
+    uint64_t n;      // output elements
+    uint64_t inner;  // size of the innermost coalesced dim (n if there is just one)
+    int mode;        // 0: inner stride 1, 1: always libm, 2: gathered in 256s
+    __device__ __forceinline__ bool uses_libm(uint64_t pos) const {
+        if (mode == 1) return true;
+        const uint64_t chunk = n < 32768 ? n : 65536;
+        const uint64_t c_lo = pos / chunk * chunk, r_lo = pos / inner * inner;
+        uint64_t lo = c_lo > r_lo ? c_lo : r_lo;
+        uint64_t hi = c_lo + chunk < r_lo + inner ? c_lo + chunk : r_lo + inner;
+        if (hi > n) hi = n;
+        if (mode == 2) {
+            lo += (pos - lo) / 256 * 256;
+            if (hi > lo + 256) hi = lo + 256;
+        }
+        return pos - lo >= ((hi - lo) & ~7ull);
+    }
+};
+
+template <class Fn> __device__ __forceinline__ float apply_unary(float v, bool libm) {
+    if constexpr (Fn::SPLIT) {
+        if (libm) return Fn::libm(v);
+    }
+    return Fn::f(v);
+}
 
 template <uint32_t OP> struct BinaryFn;
 template <> struct BinaryFn<OP_ADD> { __device__ __forceinline__ static float f(float a, float b) { return __fadd_rn(a, b); } };
@@ -94,8 +142,11 @@ __global__ void __launch_bounds__(EW_BLOCK) binary_flat_kernel(const float *__re
     }
 }
 
+// Elements at positions >= n_poly are the ones the reference computes with libm (see LibmSplit);
+// n_poly is a multiple of 8, so a 4-element work item never straddles it.
 template <class Fn>
-__global__ void __launch_bounds__(EW_BLOCK) unary_flat_kernel(const float *__restrict__ x, float *__restrict__ out, uint64_t n) {
+__global__ void __launch_bounds__(EW_BLOCK) unary_flat_kernel(const float *__restrict__ x, float *__restrict__ out, uint64_t n,
+                                                              uint64_t n_poly) {
     const uint64_t items = (n + 3) >> 2;
     const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
     float4 v[EW_UNROLL];
@@ -109,10 +160,12 @@ __global__ void __launch_bounds__(EW_BLOCK) unary_flat_kernel(const float *__res
         const uint64_t w = tile + (uint64_t)k * EW_BLOCK;
         if (w >= items) continue;
         const uint64_t i = w << 2;
+        const bool lm = i >= n_poly;
         if (i + 4 <= n) {
-            st4(out + i, make_float4(Fn::f(v[k].x), Fn::f(v[k].y), Fn::f(v[k].z), Fn::f(v[k].w)));
+            st4(out + i, make_float4(apply_unary<Fn>(v[k].x, lm), apply_unary<Fn>(v[k].y, lm), apply_unary<Fn>(v[k].z, lm),
+                                     apply_unary<Fn>(v[k].w, lm)));
         } else {
-            for (uint64_t j = i; j < n; ++j) out[j] = Fn::f(x[j]);
+            for (uint64_t j = i; j < n; ++j) out[j] = apply_unary<Fn>(x[j], lm);
         }
     }
 }
@@ -194,7 +247,7 @@ __global__ void __launch_bounds__(EW_BLOCK) binary_rows_kernel(const float *__re
 
 template <class Fn, typename I, int VEC>
 __global__ void __launch_bounds__(EW_BLOCK) unary_rows_kernel(const float *__restrict__ x, float *__restrict__ out,
-                                                              const __grid_constant__ RowsPlan<I, 1> p) {
+                                                              const __grid_constant__ RowsPlan<I, 1> p, const LibmSplit split) {
     const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
     Pack<I, VEC> v[EW_UNROLL];
     uint64_t oo[EW_UNROLL];
@@ -214,11 +267,14 @@ __global__ void __launch_bounds__(EW_BLOCK) unary_rows_kernel(const float *__res
     for (int k = 0; k < EW_UNROLL; ++k) {
         const I w = tile + (I)(k * EW_BLOCK);
         if (w < p.items) {
+            // Row starts, chunk starts and split points are all multiples of 4 when VEC is 4, so one
+            // test covers the whole work item.
+            const bool lm = Fn::SPLIT && split.uses_libm(oo[k]);
             if constexpr (VEC == 4) {
                 const float4 t = v[k].v;
-                st4(out + oo[k], make_float4(Fn::f(t.x), Fn::f(t.y), Fn::f(t.z), Fn::f(t.w)));
+                st4(out + oo[k], make_float4(apply_unary<Fn>(t.x, lm), apply_unary<Fn>(t.y, lm), apply_unary<Fn>(t.z, lm), apply_unary<Fn>(t.w, lm)));
             } else {
-                st1(out + oo[k], Fn::f(v[k].v));
+                st1(out + oo[k], apply_unary<Fn>(v[k].v, lm));
             }
         }
     }
@@ -247,7 +303,7 @@ constexpr int TILE_ROWS = 8;  // CTA is 32 x 8 threads
 template <class Fn, int NOPS>
 __global__ void __launch_bounds__(TILE *TILE_ROWS) tile_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                                float *__restrict__ out,
-                                                               const __grid_constant__ TilePlan<NOPS> p) {
+                                                               const __grid_constant__ TilePlan<NOPS> p, const LibmSplit split) {
     __shared__ float sm[NOPS][TILE][TILE + 1];
     const float *src[2] = {a, b};
     // blockIdx.x enumerates (batch, tile_f, tile_i) with tile_i fastest.
@@ -290,10 +346,11 @@ __global__ void __launch_bounds__(TILE *TILE_ROWS) tile_kernel(const float *__re
 #pragma unroll
             for (int o = 0; o < NOPS; ++o)
                 v[o] = p.transposed[o] ? sm[o][tx][ty + k] : src[o][boff[o] + (uint64_t)f * p.fstride[o] + (uint64_t)i * p.istride[o]];
+            const uint64_t pos = oboff + (uint64_t)f * p.out_fstride + i;
             float r;
             if constexpr (NOPS == 2) r = Fn::f(v[0], v[1]);
-            else r = Fn::f(v[0]);
-            out[oboff + (uint64_t)f * p.out_fstride + i] = r;
+            else r = apply_unary<Fn>(v[0], Fn::SPLIT && split.uses_libm(pos));
+            out[pos] = r;
         }
     }
 }
@@ -308,7 +365,8 @@ template <int NOPS> struct GatherPlan {
 
 template <class Fn, int NOPS>
 __global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restrict__ a, const float *__restrict__ b,
-                                                          float *__restrict__ out, const __grid_constant__ GatherPlan<NOPS> p) {
+                                                          float *__restrict__ out, const __grid_constant__ GatherPlan<NOPS> p,
+                                                          const LibmSplit split) {
     const uint64_t i = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
     if (i >= p.n) return;
     uint64_t rem = i, off[NOPS];
@@ -322,7 +380,7 @@ __global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restric
         for (int o = 0; o < NOPS; ++o) off[o] += r * p.stride[o][d];
     }
     if constexpr (NOPS == 2) out[i] = Fn::f(a[off[0]], b[off[1]]);
-    else out[i] = Fn::f(a[off[0]]);
+    else out[i] = apply_unary<Fn>(a[off[0]], Fn::SPLIT && split.uses_libm(i));
 }
 
 // ---- AXPY, FILL, RAND_NORMAL --------------------------------------------------------------------------
@@ -559,18 +617,24 @@ template <class Fn> cudaError_t run_binary(const float *a, const float *b, float
         TilePlan<2> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<2>(p, t, ctas)) {
-            B200_LAUNCH((tile_kernel<Fn, 2>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, a, b, out, t);
+            B200_LAUNCH((tile_kernel<Fn, 2>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, a, b, out, t, LibmSplit{});
             return cudaGetLastError();
         }
     }
     auto g = make_gather_plan<2>(p);
-    B200_LAUNCH((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g);
+    B200_LAUNCH((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g, LibmSplit{});
     return cudaGetLastError();
 }
 
 template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwProblem &p, cudaStream_t s) {
+    LibmSplit split{};
+    split.n = p.n;
+    split.inner = p.nd ? p.dim[p.nd - 1].size : 1;
+    const uint64_t ist = p.nd ? p.dim[p.nd - 1].stride[0] : 0;  // no dims left: the reference sees stride 0
+    split.mode = ist == 1 ? 0 : ist == 0 ? 1 : 2;
     if (p.nd <= 1 && (p.nd == 0 || p.dim[0].stride[0] == 1)) {
-        B200_LAUNCH((unary_flat_kernel<Fn>), tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, x, out, p.n);
+        const uint64_t n_poly = p.nd == 0 ? 0 : p.n - (p.n & 7);
+        B200_LAUNCH((unary_flat_kernel<Fn>), tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, x, out, p.n, n_poly);
         return cudaGetLastError();
     }
     if (p.nd >= 2 && inner_is_unit_or_zero<1>(p)) {
@@ -580,12 +644,12 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
         if (items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32)) {
             auto plan = make_rows_plan<uint32_t, 1>(p, vec);
-            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan);
-            else B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan);
+            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            else B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
         } else {
             auto plan = make_rows_plan<uint64_t, 1>(p, vec);
-            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan);
-            else B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan);
+            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            else B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
         }
         return cudaGetLastError();
     }
@@ -593,12 +657,12 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         TilePlan<1> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<1>(p, t, ctas)) {
-            B200_LAUNCH((tile_kernel<Fn, 1>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, x, nullptr, out, t);
+            B200_LAUNCH((tile_kernel<Fn, 1>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, x, nullptr, out, t, split);
             return cudaGetLastError();
         }
     }
     auto g = make_gather_plan<1>(p);
-    B200_LAUNCH((gather_kernel<Fn, 1>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, x, nullptr, out, g);
+    B200_LAUNCH((gather_kernel<Fn, 1>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, x, nullptr, out, g, split);
     return cudaGetLastError();
 }
 

@@ -310,6 +310,7 @@ uint32_t supports_op(uint32_t code) {
         case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP:
         case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV:
         case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS:
+        case PT_OP_MAX_ARGMAX_AXIS: case PT_OP_ARGMAX_COMBINE:
         case PT_OP_COPY: case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_AXPY:
             return 1;
         default:
@@ -377,6 +378,7 @@ const char *op_name(uint32_t op) {
         case PT_OP_ADD: return "ADD"; case PT_OP_SUB: return "SUB"; case PT_OP_MUL: return "MUL"; case PT_OP_DIV: return "DIV";
         case PT_OP_MATMUL: return "MATMUL"; case PT_OP_MATMUL_T: return "MATMUL_T"; case PT_OP_SUM_AXIS: return "SUM_AXIS";
         case PT_OP_MAX_AXIS: return "MAX_AXIS"; case PT_OP_ARGMAX_AXIS: return "ARGMAX_AXIS"; case PT_OP_COPY: return "COPY";
+        case PT_OP_MAX_ARGMAX_AXIS: return "MAX_ARGMAX_AXIS"; case PT_OP_ARGMAX_COMBINE: return "ARGMAX_COMBINE";
         case PT_OP_FILL: return "FILL"; case PT_OP_RAND_NORMAL: return "RAND_NORMAL"; case PT_OP_AXPY: return "AXPY";
         default: return "?";
     }
@@ -387,6 +389,55 @@ const char *op_name(uint32_t op) {
         set_err(__VA_ARGS__);               \
         return PT_STATUS_INVALID_ARGUMENT;  \
     } while (0)
+
+// The two appended ops of a sharded argmax (no counterpart in the reference): MAX_ARGMAX_AXIS has two
+// outputs and an index offset in ints[1]; ARGMAX_COMBINE reads i64 positions.
+PtStatus run_sharded_argmax(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint32_t n_in,
+                            const PtTensorDesc *outs, uint32_t n_out) {
+    cudaError_t e = cudaSuccess;
+    if (op == PT_OP_MAX_ARGMAX_AXIS) {
+        if (n_in != 1 || n_out != 2) B200_INVALID("b200: MAX_ARGMAX_AXIS takes 1 input and 2 outputs, got %u and %u", n_in, n_out);
+        const PtTensorDesc &x = ins[0];
+        if (x.dtype != PT_DTYPE_F32 || outs[0].dtype != PT_DTYPE_F32 || outs[1].dtype != PT_DTYPE_I64) {
+            set_err("b200: MAX_ARGMAX_AXIS needs an f32 input, an f32 and an i64 output");
+            return PT_STATUS_UNSUPPORTED;
+        }
+        if (attrs.ints[0] < 0 || (uint64_t)attrs.ints[0] >= x.ndim)
+            B200_INVALID("b200: MAX_ARGMAX_AXIS: axis %lld out of range for %u dims", (long long)attrs.ints[0], x.ndim);
+        const uint32_t axis = (uint32_t)attrs.ints[0];
+        uint64_t outer, inner, n0, n1;
+        const uint64_t len = x.shape[axis];
+        if (!numel(x.shape, axis, outer) || !numel(x.shape + axis + 1, x.ndim - axis - 1, inner) || !numel(outs[0].shape, outs[0].ndim, n0) ||
+            !numel(outs[1].shape, outs[1].ndim, n1) || outer * inner != n0 || n0 != n1)
+            B200_INVALID("b200: MAX_ARGMAX_AXIS: outputs do not have the reduced shape");
+        if (n0 == 0) return PT_STATUS_OK;
+        if (len == 0) B200_INVALID("b200: MAX_ARGMAX_AXIS over an empty axis has no value");
+        void *scratch = nullptr;
+        const size_t sb = reduce_scratch_bytes(REDUCE_MAX_ARGMAX, outer, len, inner, (int)device);
+        if (sb) {
+            PtStatus st = alloc_locked(d, sb, &scratch);
+            if (st != PT_STATUS_OK) return st;
+        }
+        e = launch_reduce(REDUCE_MAX_ARGMAX, (const float *)x.data, outer, len, inner, (float *)outs[0].data, (int64_t *)outs[1].data,
+                          attrs.ints[1], scratch, (int)device, d.stream);
+        if (scratch) free_locked(d, scratch);
+    } else {
+        if (n_in != 2 || n_out != 1) B200_INVALID("b200: ARGMAX_COMBINE takes 2 inputs and 1 output, got %u and %u", n_in, n_out);
+        if (ins[0].dtype != PT_DTYPE_F32 || ins[1].dtype != PT_DTYPE_I64 || outs[0].dtype != PT_DTYPE_I64) {
+            set_err("b200: ARGMAX_COMBINE needs f32 values, i64 positions and an i64 output");
+            return PT_STATUS_UNSUPPORTED;
+        }
+        uint64_t m, mo;
+        if (ins[0].ndim < 1 || !same_shape(ins[0], ins[1]) || !numel(ins[0].shape + 1, ins[0].ndim - 1, m) ||
+            !numel(outs[0].shape, outs[0].ndim, mo) || m != mo)
+            B200_INVALID("b200: ARGMAX_COMBINE: inputs must share a [G, ...] shape and the output drop its first dim");
+        if (m == 0) return PT_STATUS_OK;
+        if (ins[0].shape[0] == 0) B200_INVALID("b200: ARGMAX_COMBINE of zero candidates has no value");
+        e = launch_argmax_combine((const float *)ins[0].data, (const int64_t *)ins[1].data, ins[0].shape[0], m, (int64_t *)outs[0].data, d.stream);
+    }
+    if (e != cudaSuccess) return cuda_fail(op_name(op), e);
+    return PT_STATUS_OK;
+}
 
 // Validation follows plugins/cpu/src/lib.rs:250-334 check for check.
 PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint32_t n_in,
@@ -494,7 +545,8 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
                 PtStatus st = alloc_locked(d, sb, &scratch);
                 if (st != PT_STATUS_OK) return st;
             }
-            e = launch_reduce(kind, (const float *)x.data, outer, len, inner, o.data, scratch, (int)device, d.stream);
+            e = launch_reduce(kind, (const float *)x.data, outer, len, inner, kind == REDUCE_ARGMAX ? nullptr : (float *)o.data,
+                              kind == REDUCE_ARGMAX ? (int64_t *)o.data : nullptr, 0, scratch, (int)device, d.stream);
             if (scratch) free_locked(d, scratch);
             break;
         }
@@ -511,6 +563,7 @@ PtStatus execute(uint32_t device, uint32_t op, const PtOpAttrs *attrs, const PtT
         PtOpAttrs a{};
         if (attrs) a = *attrs;
         B200_ENTER(device);
+        if (op == PT_OP_MAX_ARGMAX_AXIS || op == PT_OP_ARGMAX_COMBINE) return run_sharded_argmax(d, device, op, a, ins, n_in, outs, n_out);
         return run(d, device, op, a, ins, n_in, outs, n_out);
     } catch (...) {
         set_err("b200: op %u raised an exception", op);

@@ -141,11 +141,12 @@ constexpr int MAX_UNROLL = 4;
 
 // inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
 // threads share one task (32: a warp per task, 256: the CTA). VEC 4 requires every task start to be
-// 16-byte aligned (the host guarantees it). Writes the value and/or the index WITHIN THE ROW.
+// 16-byte aligned (the host guarantees it). Writes the value and/or (ARG) the index within the row
+// plus idx_offset, whichever output pointers are not null.
 template <int TPT, int VEC, bool ARG>
 __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
                                                            uint64_t segs, uint64_t seg_len, float *__restrict__ out_v,
-                                                           int64_t *__restrict__ out_i) {
+                                                           int64_t *__restrict__ out_i, int64_t idx_offset) {
     constexpr int PER_CTA = MAX_CTA / TPT;
     const uint64_t t = (uint64_t)blockIdx.x * PER_CTA + threadIdx.x / TPT;
     const int lane = threadIdx.x % TPT;
@@ -217,27 +218,27 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
     }
     if (live && lane == 0) {
         if (out_v) out_v[t] = bv;
-        if (ARG && out_i) out_i[t] = (int64_t)bi;
+        if (ARG && out_i) out_i[t] = (int64_t)bi + idx_offset;
     }
 }
 
-// Pass 2 for rows split into several segments: thread per row scans its segment results in order.
-template <bool ARG>
+// Pass 2 for rows split into several segments: thread per row scans its segment results in order and
+// writes the value and/or the index (plus idx_offset), whichever output pointers are not null.
 __global__ void __launch_bounds__(256) max_combine_kernel(const float *__restrict__ pv, const int64_t *__restrict__ pi, uint64_t outer,
-                                                          uint64_t segs, float *__restrict__ out_v, int64_t *__restrict__ out_i) {
+                                                          uint64_t segs, float *__restrict__ out_v, int64_t *__restrict__ out_i,
+                                                          int64_t idx_offset) {
     const uint64_t r = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (r >= outer) return;
     float bv = pv[r * segs];
     uint64_t bs = 0;
     for (uint64_t s = 1; s < segs; ++s) scan_step(pv[r * segs + s], s, bv, bs);
-    if (ARG) out_i[r] = pi[r * segs + bs];
-    else out_v[r] = bv;
+    if (out_i) out_i[r] = pi[r * segs + bs] + idx_offset;
+    if (out_v) out_v[r] = bv;
 }
 
 // inner > 1: thread per output column scans rows j in order.
-template <bool ARG>
 __global__ void __launch_bounds__(256) max_cols_kernel(const float *__restrict__ x, uint64_t total, uint64_t len, uint64_t inner,
-                                                       float *__restrict__ out_v, int64_t *__restrict__ out_i) {
+                                                       float *__restrict__ out_v, int64_t *__restrict__ out_i, int64_t idx_offset) {
     const uint64_t t = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (t >= total) return;
     const uint64_t o = t / inner, i = t - o * inner;
@@ -253,8 +254,24 @@ __global__ void __launch_bounds__(256) max_cols_kernel(const float *__restrict__
         for (int u = 0; u < COL_UNROLL; ++u) scan_step(v[u], j + u, bv, bi);
     }
     for (; j < len; ++j) scan_step(ldf(p + j * inner), j, bv, bi);
-    if (ARG) out_i[t] = (int64_t)bi;
-    else out_v[t] = bv;
+    if (out_i) out_i[t] = (int64_t)bi + idx_offset;
+    if (out_v) out_v[t] = bv;
+}
+
+// Combine of a sharded argmax: vals/idx are [g, m], one row of candidates per shard; per column the
+// best candidate's position is kept (NaN wins, then the larger value, then the lower position).
+__global__ void __launch_bounds__(256) argmax_combine_kernel(const float *__restrict__ vals, const int64_t *__restrict__ idx, uint64_t g,
+                                                             uint64_t m, int64_t *__restrict__ out) {
+    const uint64_t j = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (j >= m) return;
+    float bv = vals[j];
+    uint64_t bi = (uint64_t)idx[j];
+    for (uint64_t r = 1; r < g; ++r) {
+        const float v = vals[r * m + j];
+        const uint64_t i = (uint64_t)idx[r * m + j];
+        if (vi_better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    out[j] = (int64_t)bi;
 }
 
 // ---- host-side planning ------------------------------------------------------------------------------------
@@ -300,15 +317,15 @@ size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint6
     if (m.segs == 1) return 0;
     const uint64_t tasks = outer * m.segs;
     // values, then (16-byte aligned) indices
-    return ((tasks * 4 + 15) & ~15ull) + (kind == REDUCE_ARGMAX ? tasks * 8 : 0);
+    return ((tasks * 4 + 15) & ~15ull) + (kind != REDUCE_MAX ? tasks * 8 : 0);
 }
 
-cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, void *out, void *scratch,
-                          int device, cudaStream_t s) {
+cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
+                          int64_t idx_offset, void *scratch, int device, cudaStream_t s) {
     const uint64_t total = outer * inner;
     if (total == 0) return cudaSuccess;
     if (kind == REDUCE_SUM) {
-        float *o = (float *)out;
+        float *o = out_v;
         if (len == 0) return launch_fill(o, total, 0.0f, s);  // reduce.rs:106-109
         if (inner == 1) {
             if (len < 32) {
@@ -324,37 +341,41 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
         B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
         return cudaGetLastError();
     }
-    const bool arg = kind == REDUCE_ARGMAX;
-    float *ov = arg ? nullptr : (float *)out;
-    int64_t *oi = arg ? (int64_t *)out : nullptr;
+    // MAX writes values, ARGMAX positions, MAX_ARGMAX both.
+    const bool arg = kind != REDUCE_MAX;
+    float *ov = kind == REDUCE_ARGMAX ? nullptr : out_v;
+    int64_t *oi = arg ? out_i : nullptr;
     if (inner != 1) {
-        if (arg) B200_LAUNCH(max_cols_kernel<true>, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi);
-        else B200_LAUNCH(max_cols_kernel<false>, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi);
+        B200_LAUNCH(max_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi, idx_offset);
         return cudaGetLastError();
     }
     const MaxPlan m = plan_max(outer, len, sm_count(device));
     const uint64_t tasks = outer * m.segs;
     float *pv = ov;
     int64_t *pi = oi;
-    if (m.segs > 1) {
+    int64_t off1 = idx_offset;
+    if (m.segs > 1) {  // pass 1 writes per-segment results (positions within the row) to scratch
         pv = (float *)scratch;
         pi = arg ? (int64_t *)((char *)scratch + ((tasks * 4 + 15) & ~15ull)) : nullptr;
+        off1 = 0;
     }
     const unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
-#define B200_MAX_CASE(TPT, VEC)                                                                                          \
-    if (m.tpt == TPT && m.vec == VEC) {                                                                                  \
-        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi); \
-        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi);    \
+#define B200_MAX_CASE(TPT, VEC)                                                                                                       \
+    if (m.tpt == TPT && m.vec == VEC) {                                                                                               \
+        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1);  \
+        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1);     \
     }
     B200_MAX_CASE(32, 1)
     B200_MAX_CASE(32, 4)
     B200_MAX_CASE(256, 1)
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
-    if (m.segs > 1) {
-        if (arg) B200_LAUNCH(max_combine_kernel<true>, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi);
-        else B200_LAUNCH(max_combine_kernel<false>, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi);
-    }
+    if (m.segs > 1) B200_LAUNCH(max_combine_kernel, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s) {
+    B200_LAUNCH(argmax_combine_kernel, (unsigned)((m + 255) / 256), 256, 0, s, vals, idx, g, m, out);
     return cudaGetLastError();
 }
 

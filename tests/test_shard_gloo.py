@@ -1,0 +1,110 @@
+"""The sharding layer on CPU: world_size 2 and 3 over gloo, with the CPU oracle as each rank's plugin.
+
+Checks the host logic of ``pytorches_b200.shard``: row partitioning (uneven splits included),
+elementwise ops on shards equal to the unsharded op, and reductions that cross the sharded dimension
+equal to the fixed-order combine of the per-rank partials (bit-exact) and to the unsharded result
+(exact for max/argmax, within the summation-order tolerance for sum/mean).
+"""
+
+import math
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_SO = os.path.join(ROOT, "oracle", "_build", "pytorches_plugin_cpuref.so")
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, n: int):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["PYTORCHES_CPU_THREADS"] = "2"
+    from harness import lcg_data
+    from pytorches_b200.abi import Plugin, op
+    from pytorches_b200.core import Device, Tensor
+    from pytorches_b200.shard import ShardGroup, split_rows
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        plugin = Plugin(ORACLE_SO)
+        dev = Device(plugin, 0)
+        g = ShardGroup(dev, rank, world)
+        bits = lambda a: np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+        # ---- full-tensor reductions over n elements, ties and a clear maximum in a late shard ----
+        x = (np.round(lcg_data(n, 7) * 32) / 32).astype(np.float32)
+        x[n - 3] = 5.0
+        x[n // 2] = 5.0  # the same maximum earlier: argmax must be the lower position, n // 2
+        start, count = split_rows(n, rank, world)
+        assert sum(split_rows(n, r, world)[1] for r in range(world)) == n
+        local = Tensor.from_numpy(x[start:start + count], dev)
+        full = Tensor.from_numpy(x, dev)
+
+        partials = []
+        for r in range(world):  # every rank recomputes all partials locally to know the expected combine
+            s, c = split_rows(n, r, world)
+            partials.append(Tensor.from_numpy(x[s:s + c], dev).sum().numpy().reshape(1))
+        want_sum = Tensor.from_numpy(np.concatenate(partials), dev).raw_sum_axis(0).numpy()
+        got_sum = g.sum(local).numpy()
+        assert bits(got_sum) == bits(want_sum), (got_sum, want_sum)
+        ref = x.astype(np.float64).sum()
+        assert abs(float(got_sum) - ref) <= 1e-5 * math.log2(n) * np.abs(x.astype(np.float64)).sum()
+        got_mean = g.mean(local, n).numpy()
+        assert bits(got_mean) == bits(np.float32(want_sum) / np.float32(n))
+
+        assert bits(g.max(local).numpy()) == bits(full.max().numpy())
+        assert g.argmax(local, start).numpy() == full.argmax().numpy() == n // 2
+
+        # all ranks hold the same combined results
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (got_sum.tobytes(), got_mean.tobytes()))
+        assert all(item == gathered[0] for item in gathered)
+
+        # ---- a [rows, cols] problem: elementwise on shards, then a column sum across shards ----
+        rows, cols = 37, 24
+        A = lcg_data(rows * cols, 1).reshape(rows, cols)
+        b = lcg_data(cols, 2).reshape(1, cols)       # leading dim 1: replicated
+        s_col = lcg_data(rows, 3).reshape(rows, 1)   # leading dim sharded like A
+        r0, rc = split_rows(rows, rank, world)
+        out_local = (Tensor.from_numpy(A[r0:r0 + rc], dev) + Tensor.from_numpy(b, dev)).relu() * Tensor.from_numpy(s_col[r0:r0 + rc], dev)
+        out_full = (Tensor.from_numpy(A, dev) + Tensor.from_numpy(b, dev)).relu() * Tensor.from_numpy(s_col, dev)
+        assert np.array_equal(bits(out_local.numpy()), bits(out_full.numpy()[r0:r0 + rc]))
+        db = g.sum_axis0(out_local).numpy()
+        parts = []
+        for r in range(world):
+            s, c = split_rows(rows, r, world)
+            parts.append(out_full.numpy()[s:s + c].astype(np.float32))
+        want_db = Tensor.from_numpy(
+            np.stack([Tensor.from_numpy(p, dev).raw_sum_axis(0).numpy() for p in parts]), dev).raw_sum_axis(0).numpy()
+        assert np.array_equal(bits(db), bits(want_db))
+        assert np.allclose(db, out_full.numpy().astype(np.float64).sum(axis=0), rtol=0, atol=1e-5 * np.abs(out_full.numpy()).sum(axis=0).max())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n", [(2, 200_001), (3, 70_000)])
+def test_sharded_ops_over_gloo(oracle, world, n):
+    mp.spawn(_worker, args=(world, _free_port(), n), nprocs=world, join=True)
+
+
+def test_split_rows_covers_everything():
+    from pytorches_b200.shard import split_rows
+
+    for n in (0, 1, 7, 8, 12, 1 << 28):
+        for world in (1, 2, 3, 4, 8):
+            spans = [split_rows(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and sum(c for _, c in spans) == n
+            for (s0, c0), (s1, _) in zip(spans, spans[1:]):
+                assert s0 + c0 == s1
+            assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
