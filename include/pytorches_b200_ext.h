@@ -32,6 +32,36 @@ void *pytorches_b200_stream(uint32_t device);
  */
 uint64_t pytorches_b200_kernel_launches(void);
 
+/*
+ * Sum of the n f32 values at `x` into `out[0]`, for hosts that cannot allocate device memory when
+ * they call: a process that handed the whole GPU to its own memory pool at start-up (a serving
+ * process, another framework's caching allocator) has nothing left for a library to allocate from,
+ * and a host with a latency budget may forbid allocator calls on its hot path because they can stall
+ * every stream of the device. The vtable's SUM_AXIS takes its inter-pass scratch from the plugin's
+ * allocator; this entry point keeps that scratch in a fixed 256 KiB array inside the library
+ * instead (every GPU that loads the library holds the array until the process exits) and calls no
+ * allocation or free routine of CUDA, of this plugin, or of any other library.
+ *
+ * It has no counterpart in the reference, whose ABI always lets a plugin allocate.
+ *
+ *   device  index of the GPU that `x` and `out` live on
+ *   x, out  device pointers owned by the caller (any memory of that GPU, not only the plugin's)
+ *   n       element count; at most 2^32 (the array holds one partial sum per 65536 elements).
+ *           Larger n is refused with PT_STATUS_INVALID_ARGUMENT and a message naming the limit,
+ *           readable through the vtable's last_error(); nothing is launched.
+ *   stream  the cudaStream_t to enqueue on (NULL is CUDA's default stream); the call returns
+ *           once the kernels are queued, like the vtable's execute
+ *
+ * The result is bit-identical to SUM_AXIS over a 1-D tensor of the same data. Returns a PtStatus.
+ *
+ * The first call on each device looks up the array's address on that device (one
+ * cudaGetSymbolAddress); make that first call outside any stream capture. All calls on one GPU share
+ * the one array: two calls whose kernels can overlap on the GPU (different streams, no ordering
+ * between them) race on it and both results are undefined. Calls ordered on one stream are safe,
+ * and no call depends on what an earlier one left in the array: each overwrites the slots it reads.
+ */
+int32_t pytorches_b200_sum_noalloc(uint32_t device, const float *x, uint64_t n, float *out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

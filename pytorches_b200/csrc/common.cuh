@@ -18,6 +18,9 @@ extern std::atomic<uint64_t> g_kernel_launches;
 // B200 has 148 SMs; grids of persistent kernels are sized from the queried count at run time.
 int sm_count(int device);
 
+// Stores `msg` as the calling thread's last error (what the vtable's last_error() returns).
+void set_last_error(const char *msg);
+
 // Exact floor division by a runtime constant. For 32-bit operands: Lemire's method,
 // floor(n/d) = hi64(ceil(2^64/d) * n) for every n, d < 2^32 (d > 1). For 64-bit operands the
 // hardware-emulated division is used; that path only runs for tensors of 2^32 or more work items.

@@ -579,6 +579,8 @@ const PtPluginVTable VTABLE = {
 
 }  // namespace
 
+void set_last_error(const char *msg) { set_err("%s", msg); }
+
 int sm_count(int device) {
     if (device < 0) (void)cudaGetDevice(&device);
     if (device >= 0 && device < MAX_DEVICES && g_dev[device].sms) return g_dev[device].sms;

@@ -15,6 +15,9 @@
 // ties). max is order-independent, so these use float4 loads and a two-pass (value, index) combine.
 //
 // All kernels are pure HBM streaming: every load of a thread's batch is issued before the first use.
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -380,3 +383,100 @@ cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_
 }
 
 }  // namespace b200
+
+// ---- a sum for callers that must not allocate ------------------------------------------------------------
+//
+// pytorches_b200_sum_noalloc is the full-tensor SUM_AXIS above with one difference: the per-block
+// partial sums that pass 1 hands to pass 2 live in a fixed array inside this library instead of a
+// block obtained from the plugin's allocator. It exists for hosts that may not create device memory
+// at the moment they need a sum: a process that gave all of the GPU's memory to its own pool at
+// start-up (an inference server, another framework's caching allocator), or one under a rule that
+// nothing on its hot path may call into the driver's allocator because such a call can stall the
+// whole device. Those hosts own the input and output buffers already; the only thing they lacked was
+// the scratch, and here it costs no call at all.
+//
+// The array is 256 KiB of every GPU that loads this library, held until the process exits. It has
+// room for 65536 block sums, which bounds the input at 2^32 elements (16 GiB of f32).
+namespace b200 {
+namespace {
+
+constexpr uint64_t NOALLOC_MAX_BLOCKS = 1ull << 16;
+constexpr uint64_t NOALLOC_MAX_ELEMS = NOALLOC_MAX_BLOCKS * SUM_BLOCK;  // 2^32
+
+// Device-side storage. In host code this name is only a handle for cudaGetSymbolAddress, never a
+// pointer a kernel could use.
+static __device__ __align__(256) float g_noalloc_partials[NOALLOC_MAX_BLOCKS];
+
+std::mutex g_noalloc_mu;
+float *g_noalloc_ptr[64] = {};  // per device: the array's address in that device's memory
+
+}  // namespace
+}  // namespace b200
+
+extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noalloc(uint32_t device, const float *x, uint64_t n,
+                                                                                    float *out, void *stream) {
+    using namespace b200;
+    try {
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || (int)device >= count || device >= 64) {
+            (void)cudaGetLastError();
+            set_last_error("b200: sum_noalloc: no such device");
+            return 3;  // PT_STATUS_INVALID_ARGUMENT
+        }
+        if (n > NOALLOC_MAX_ELEMS) {
+            char msg[160];
+            std::snprintf(msg, sizeof msg, "b200: sum_noalloc: %llu elements exceed the built-in scratch (at most %llu)",
+                          (unsigned long long)n, (unsigned long long)NOALLOC_MAX_ELEMS);
+            set_last_error(msg);
+            return 3;
+        }
+        if (!out || (n && !x)) {
+            set_last_error("b200: sum_noalloc: null input or output");
+            return 3;
+        }
+        cudaError_t e = cudaSetDevice((int)device);
+        float *partials = nullptr;
+        if (e == cudaSuccess) {
+            // Once per device, with that device current: ask the runtime where the array lives there.
+            std::lock_guard<std::mutex> lock(g_noalloc_mu);
+            if (!g_noalloc_ptr[device]) {
+                void *p = nullptr;
+                e = cudaGetSymbolAddress(&p, g_noalloc_partials);
+                if (e == cudaSuccess) g_noalloc_ptr[device] = (float *)p;
+            }
+            partials = g_noalloc_ptr[device];
+        }
+        if (e != cudaSuccess) {
+            char msg[160];
+            std::snprintf(msg, sizeof msg, "b200: sum_noalloc: device set-up failed: %s", cudaGetErrorString(e));
+            (void)cudaGetLastError();
+            set_last_error(msg);
+            return 4;  // PT_STATUS_INTERNAL
+        }
+        cudaStream_t s = (cudaStream_t)stream;
+        if (n == 0) {
+            e = launch_fill(out, 1, 0.0f, s);  // the sum of nothing is 0.0 (reduce.rs:106-109)
+        } else if (n < 32) {
+            B200_LAUNCH(sum_short_rows_kernel, 1, 256, 0, s, x, (uint64_t)1, (uint32_t)n, out);
+            e = cudaGetLastError();
+        } else {
+            // Pass 1 overwrites partials[0 .. blocks) completely before pass 2 reads them, so what an
+            // earlier call left in the array never matters and nothing needs clearing.
+            const uint64_t blocks = (n + SUM_BLOCK - 1) / SUM_BLOCK;
+            float *dst = blocks == 1 ? out : partials;
+            B200_LAUNCH(sum_rows_kernel, (unsigned)((blocks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, blocks, n, blocks, dst);
+            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, 1, 32, 0, s, (const float *)partials, blocks, out);
+            e = cudaGetLastError();
+        }
+        if (e != cudaSuccess) {
+            char msg[160];
+            std::snprintf(msg, sizeof msg, "b200: sum_noalloc: launch failed: %s", cudaGetErrorString(e));
+            set_last_error(msg);
+            return 4;
+        }
+        return 0;
+    } catch (...) {
+        return 4;
+    }
+}
+
