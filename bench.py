@@ -309,7 +309,7 @@ def main():
     if op_ev:
         sum_ms = statistics.mean(a.elapsed_time(b) for a, b in op_ev)
         achieved = 4 * N_ELEMS / (sum_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "sum_rows_kernel (+ sum_combine_kernel): one SUM_AXIS over 2^28 f32", "achieved": round(achieved, 1),
+        roofline = {"bound": "hbm", "kernel": "sum_rows_tma_kernel (+ sum_combine_kernel): one SUM_AXIS over 2^28 f32", "achieved": round(achieved, 1),
                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_8TBps": round(achieved / 8000.0, 4),
                     "algorithmic_bytes_per_launch": 4 * N_ELEMS, "ms_per_launch": round(sum_ms, 5), "traffic": None}
     cpu = None

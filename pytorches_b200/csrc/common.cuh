@@ -76,6 +76,9 @@ enum ReduceKind : int { REDUCE_SUM = 0, REDUCE_MAX = 1, REDUCE_ARGMAX = 2, REDUC
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
 cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v,
                           int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s);
+// Kernels with bounded device-side waits report an expired wait in a host-visible word; this returns
+// and clears it (0 = nothing happened).
+int take_reduce_status();
 // Per column of [g, m] candidates (value, position), the position of the best one.
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s);
 

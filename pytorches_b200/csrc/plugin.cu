@@ -198,6 +198,10 @@ void free_buf(uint32_t device, void *ptr) {
 // A deferred fault is reported by the next call that can (docs/plugin-abi.md:155-156).
 PtStatus finish_blocking(DeviceState &d, const char *what) {
     cudaError_t e = cudaStreamSynchronize(d.stream);
+    if (e == cudaSuccess && take_reduce_status() != 0) {
+        set_err("b200: %s: a reduction kernel gave up on a bounded device-side wait; its result is invalid", what);
+        return PT_STATUS_INTERNAL;
+    }
     if (e == cudaSuccess && d.deferred != cudaSuccess) {
         e = d.deferred;
         d.deferred = cudaSuccess;

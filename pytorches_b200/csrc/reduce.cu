@@ -70,6 +70,119 @@ __global__ void __launch_bounds__(32 * SUM_WARPS) sum_rows_kernel(const float *_
     if (lane == 0) dst[t] = blocks == 1 ? __fadd_rn(0.0f, s) : s;
 }
 
+// ---- pass 1 for long rows: TMA-staged -------------------------------------------------------------------
+// The order constraint fixes the parallelism at one warp per 65536 elements, too few warps to keep
+// HBM busy with register loads. So the warp lets the TMA engine do the loading: lane 0 keeps
+// TMA_STAGES bulk copies of TMA_CHUNK floats (16 KiB each, 64 KiB per warp) in flight into a
+// shared-memory ring, each completing on an mbarrier; the warp then reads a landed chunk at stride 32
+// (lane j takes words j, j+32, ...: conflict-free, and exactly "element i goes to slot i mod 32") and
+// adds in order. One warp per CTA, three CTAs per SM by shared memory: 192 KiB in flight per SM.
+// Bulk copies need 16-byte aligned sources; the host picks this kernel only when every block start is.
+//
+// Every wait is bounded. If a barrier does not complete within the limit the warp gives its other
+// copies in flight the same bounded chance to land, records WAIT_EXPIRED in *status (pinned host
+// memory the next blocking call inspects) and returns without a result.
+constexpr int TMA_STAGES = 4;
+constexpr uint32_t TMA_CHUNK = 4096;  // floats per bulk copy
+constexpr uint32_t TMA_CHUNK_BYTES = TMA_CHUNK * 4;
+constexpr size_t TMA_SMEM = (size_t)TMA_STAGES * TMA_CHUNK_BYTES;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait calls before giving up (each may block briefly)
+constexpr int STATUS_WAIT_EXPIRED = 1;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (uint32_t tries = 0; tries < WAIT_LIMIT; ++tries)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Bulk copy from global memory into this CTA's own shared memory.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
+                                                          float *__restrict__ dst, int *status) {
+    extern __shared__ __align__(128) unsigned char tma_smem[];
+    __shared__ uint64_t bars[TMA_STAGES];
+    float *ring = reinterpret_cast<float *>(tma_smem);
+    const uint64_t t = blockIdx.x;
+    const int lane = threadIdx.x;
+    if (lane == 0) {
+        for (int s = 0; s < TMA_STAGES; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const uint64_t row = t / blocks, b = t - row * blocks;
+    const uint64_t lo = b * SUM_BLOCK;
+    const uint32_t m = (uint32_t)(len - lo < SUM_BLOCK ? len - lo : SUM_BLOCK);
+    const float *p = x + row * len + lo;
+    const uint32_t chunks = m / TMA_CHUNK;
+    if (lane == 0) {
+        for (uint32_t c = 0; c < TMA_STAGES && c < chunks; ++c) {
+            mbar_expect_tx(&bars[c], TMA_CHUNK_BYTES);
+            bulk_load(ring + (size_t)c * TMA_CHUNK, p + (size_t)c * TMA_CHUNK, TMA_CHUNK_BYTES, &bars[c]);
+        }
+    }
+    float s = 0.0f;
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const int st = c % TMA_STAGES;
+        if (!mbar_wait_bounded(&bars[st], (c / TMA_STAGES) & 1)) {
+            // Give the copies still in flight (chunks c+1 .. c+STAGES-1) their bounded chance, then stop.
+            for (uint32_t d = c + 1; d < chunks && d < c + TMA_STAGES; ++d) (void)mbar_wait_bounded(&bars[d % TMA_STAGES], (d / TMA_STAGES) & 1);
+            if (lane == 0) {
+                *(volatile int *)status = STATUS_WAIT_EXPIRED;
+                __threadfence_system();
+            }
+            return;
+        }
+        const float *buf = ring + (size_t)st * TMA_CHUNK;
+#pragma unroll 2
+        for (uint32_t k = 0; k < TMA_CHUNK / 32; k += 32) {
+            float v[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) v[u] = buf[lane + 32 * (k + u)];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) s = __fadd_rn(s, v[u]);
+        }
+        __syncwarp();  // every lane is done reading this stage before it is refilled
+        if (lane == 0 && c + TMA_STAGES < chunks) {
+            mbar_expect_tx(&bars[st], TMA_CHUNK_BYTES);
+            bulk_load(ring + (size_t)st * TMA_CHUNK, p + (size_t)(c + TMA_STAGES) * TMA_CHUNK, TMA_CHUNK_BYTES, &bars[st]);
+        }
+    }
+    // What is left of the block (fewer than TMA_CHUNK elements) continues the same slots with loads.
+    const uint32_t m32 = m & ~31u;
+    for (uint32_t k = chunks * TMA_CHUNK + lane; k < m32; k += 32) s = __fadd_rn(s, ldf(p + k));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 8));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 16));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 4));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 2));
+    s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 1));
+    if (lane == 0) {
+        for (uint32_t i = m32; i < m; ++i) s = __fadd_rn(s, p[i]);
+        dst[t] = blocks == 1 ? __fadd_rn(0.0f, s) : s;
+    }
+}
+
 // Rows shorter than 32 elements never fill a slot: the reference adds them one by one to 0.0.
 __global__ void __launch_bounds__(256) sum_short_rows_kernel(const float *__restrict__ x, uint64_t outer, uint32_t len,
                                                              float *__restrict__ out) {
@@ -81,21 +194,45 @@ __global__ void __launch_bounds__(256) sum_short_rows_kernel(const float *__rest
     out[r] = __fadd_rn(0.0f, s);
 }
 
-// Pass 2, inner == 1: out[row] = ((0.0 + p[0]) + p[1]) + ... in block order. One warp per row stages
-// the partials through shared memory with coalesced loads; lane 0 does the ordered chain.
-constexpr int COMBINE_STAGE = 2048;
-__global__ void __launch_bounds__(32) sum_combine_kernel(const float *__restrict__ partial, uint64_t blocks, float *__restrict__ out) {
-    __shared__ float stage[COMBINE_STAGE];
+// Pass 2, inner == 1: out[row] = ((0.0 + p[0]) + p[1]) + ... in block order. A CTA per row stages the
+// partials through shared memory (all threads, all loads of a stage in flight at once); thread 0 runs
+// the ordered chain. The chain is inherently serial, one add latency per partial, so the 32 values of
+// the next step are fetched from shared memory while the current 32 are being added.
+constexpr int COMBINE_THREADS = 256;
+constexpr int COMBINE_STAGE = 4096;
+__global__ void __launch_bounds__(COMBINE_THREADS) sum_combine_kernel(const float *__restrict__ partial, uint64_t blocks,
+                                                                      float *__restrict__ out) {
+    __shared__ float stage[COMBINE_STAGE + 32];
     const uint64_t row = blockIdx.x;
     const float *p = partial + row * blocks;
     float s = 0.0f;
     for (uint64_t base = 0; base < blocks; base += COMBINE_STAGE) {
         const uint32_t m = (uint32_t)(blocks - base < COMBINE_STAGE ? blocks - base : COMBINE_STAGE);
-        for (uint32_t i = threadIdx.x; i < m; i += 32) stage[i] = p[base + i];
-        __syncwarp();
-        if (threadIdx.x == 0)
-            for (uint32_t i = 0; i < m; ++i) s = __fadd_rn(s, stage[i]);
-        __syncwarp();
+        float v[COMBINE_STAGE / COMBINE_THREADS];
+#pragma unroll
+        for (int u = 0; u < COMBINE_STAGE / COMBINE_THREADS; ++u) {
+            const uint32_t i = threadIdx.x + COMBINE_THREADS * u;
+            v[u] = i < m ? p[base + i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < COMBINE_STAGE / COMBINE_THREADS; ++u) stage[threadIdx.x + COMBINE_THREADS * u] = v[u];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const uint32_t full = m & ~31u;
+            float cur[32], nxt[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) cur[u] = stage[u];
+            for (uint32_t i = 0; i < full; i += 32) {
+#pragma unroll
+                for (int u = 0; u < 32; ++u) nxt[u] = stage[i + 32 + u];  // stage has 32 floats of slack
+#pragma unroll
+                for (int u = 0; u < 32; ++u) s = __fadd_rn(s, cur[u]);
+#pragma unroll
+                for (int u = 0; u < 32; ++u) cur[u] = nxt[u];
+            }
+            for (uint32_t i = full; i < m; ++i) s = __fadd_rn(s, stage[i]);
+        }
+        __syncthreads();
     }
     if (threadIdx.x == 0) out[row] = s;
 }
@@ -225,18 +362,41 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
     }
 }
 
-// Pass 2 for rows split into several segments: thread per row scans its segment results in order and
-// writes the value and/or the index (plus idx_offset), whichever output pointers are not null.
+// Pass 2 for rows split into several segments: a CTA per row. Each thread scans a strided share of
+// the row's segment results, then the CTA picks the best (value, segment) pair: the lowest segment
+// wins ties, so the lowest position does. Writes the value and/or the index (plus idx_offset),
+// whichever output pointers are not null.
 __global__ void __launch_bounds__(256) max_combine_kernel(const float *__restrict__ pv, const int64_t *__restrict__ pi, uint64_t outer,
                                                           uint64_t segs, float *__restrict__ out_v, int64_t *__restrict__ out_i,
                                                           int64_t idx_offset) {
-    const uint64_t r = (uint64_t)blockIdx.x * 256 + threadIdx.x;
-    if (r >= outer) return;
-    float bv = pv[r * segs];
-    uint64_t bs = 0;
-    for (uint64_t s = 1; s < segs; ++s) scan_step(pv[r * segs + s], s, bv, bs);
-    if (out_i) out_i[r] = pi[r * segs + bs] + idx_offset;
-    if (out_v) out_v[r] = bv;
+    __shared__ float sv[8];
+    __shared__ uint64_t ss[8];
+    const uint64_t r = blockIdx.x;
+    float bv = __int_as_float(0xff800000);
+    uint64_t bs = threadIdx.x < segs ? threadIdx.x : ~0ull;
+    for (uint64_t s = threadIdx.x; s < segs; s += 256) scan_step(pv[r * segs + s], s, bv, bs);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const uint64_t os = __shfl_xor_sync(0xffffffffu, bs, d);
+        if (vi_better(ov, os, bv, bs)) { bv = ov; bs = os; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; ss[threadIdx.x >> 5] = bs; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        bv = threadIdx.x < 8 ? sv[threadIdx.x] : __int_as_float(0xff800000);
+        bs = threadIdx.x < 8 ? ss[threadIdx.x] : ~0ull;
+#pragma unroll
+        for (int d = 4; d >= 1; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+            const uint64_t os = __shfl_xor_sync(0xffffffffu, bs, d);
+            if (vi_better(ov, os, bv, bs)) { bv = ov; bs = os; }
+        }
+        if (threadIdx.x == 0) {
+            if (out_i) out_i[r] = pi[r * segs + bs] + idx_offset;
+            if (out_v) out_v[r] = bv;
+        }
+    }
 }
 
 // inner > 1: thread per output column scans rows j in order.
@@ -286,7 +446,7 @@ struct MaxPlan {
     uint64_t seg_len;  // elements per segment (multiple of 4)
 };
 
-MaxPlan plan_max(uint64_t outer, uint64_t len, int sms) {
+MaxPlan plan_max(uint64_t outer, uint64_t len, int /*sms*/) {
     MaxPlan m;
     m.vec = (len % 4 == 0 || outer == 1) ? 4 : 1;
     if (len <= 16384) {
@@ -295,19 +455,54 @@ MaxPlan plan_max(uint64_t outer, uint64_t len, int sms) {
         m.seg_len = (len + 3) & ~3ull;
         return m;
     }
+    // Long rows: a 256-thread CTA per 16384-element segment (four batches of four float4 per thread).
+    // Measured on a 1 GiB row: segments of 8 Ki to 256 Ki elements all run within 3% of each other and
+    // 16 Ki is the best; 4 Ki pays too much per-CTA epilogue, 1 Mi leaves too few CTAs.
     m.tpt = 256;
-    const uint64_t target = (uint64_t)sms * 16;  // CTAs wanted in flight
-    uint64_t segs = (target + outer - 1) / outer;
-    const uint64_t max_segs = (len + 16383) / 16384;
-    if (segs > max_segs) segs = max_segs;
-    if (segs < 1) segs = 1;
-    uint64_t seg_len = (len + segs - 1) / segs;
-    seg_len = (seg_len + 1023) & ~1023ull;
-    m.seg_len = seg_len;
-    m.segs = (len + seg_len - 1) / seg_len;
+    m.seg_len = 16384;
+    m.segs = (len + m.seg_len - 1) / m.seg_len;
     return m;
 }
 
+}  // namespace
+
+// One word of pinned, device-visible host memory in which kernels report a bounded wait that ran out
+// (0 = nothing to report). Written by the device, read by the host at the next blocking call.
+int *reduce_status_word() {
+    static int *word = [] {
+        int *p = nullptr;
+        if (cudaHostAlloc((void **)&p, sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return (int *)nullptr;
+        }
+        *p = 0;
+        return p;
+    }();
+    return word;
+}
+
+int take_reduce_status() {
+    int *w = reduce_status_word();
+    if (!w) return 0;
+    const int v = *(volatile int *)w;
+    if (v) *(volatile int *)w = 0;
+    return v;
+}
+
+namespace {
+// Opts the TMA kernel into its 64 KiB of dynamic shared memory, once per device.
+bool tma_kernel_ready(int device) {
+    static std::mutex mu;
+    static bool done[64] = {}, ok[64] = {};
+    if (device < 0 || device >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[device]) {
+        done[device] = true;
+        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess;
+        if (!ok[device]) (void)cudaGetLastError();
+    }
+    return ok[device];
+}
 }  // namespace
 
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device) {
@@ -337,8 +532,14 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
             }
             const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK, tasks = outer * blocks;
             float *dst = blocks == 1 ? o : (float *)scratch;
-            B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
-            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, 32, 0, s, (const float *)scratch, blocks, o);
+            // Long rows whose block starts are 16-byte aligned take the TMA-staged kernel.
+            int *status = (len >= 8 * TMA_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word() : nullptr;
+            if (status && tma_kernel_ready(device)) {
+                B200_LAUNCH(sum_rows_tma_kernel, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status);
+            } else {
+                B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
+            }
+            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, COMBINE_THREADS, 0, s, (const float *)scratch, blocks, o);
             return cudaGetLastError();
         }
         B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
@@ -373,7 +574,7 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
     B200_MAX_CASE(256, 1)
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
-    if (m.segs > 1) B200_LAUNCH(max_combine_kernel, (unsigned)((outer + 255) / 256), 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
+    if (m.segs > 1) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
     return cudaGetLastError();
 }
 
@@ -465,7 +666,7 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noa
             const uint64_t blocks = (n + SUM_BLOCK - 1) / SUM_BLOCK;
             float *dst = blocks == 1 ? out : partials;
             B200_LAUNCH(sum_rows_kernel, (unsigned)((blocks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, blocks, n, blocks, dst);
-            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, 1, 32, 0, s, (const float *)partials, blocks, out);
+            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, 1, COMBINE_THREADS, 0, s, (const float *)partials, blocks, out);
             e = cudaGetLastError();
         }
         if (e != cudaSuccess) {

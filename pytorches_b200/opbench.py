@@ -109,7 +109,7 @@ def main():
     torch.cuda.set_device(args.device)
     stream = torch.cuda.ExternalStream(get_stream(args.device), device=torch.device("cuda", args.device))
 
-    cases = [(args.op, args.elements)]
+    cases = [(name, args.elements) for name in (OPS if args.op == "all" else args.op.split(","))]
     if args.sweep:
         cases = [(name, (1 << 18) * 4 ** k) for name in OPS for k in range(7)]
     for name, n in cases:
