@@ -355,6 +355,105 @@ __global__ void __launch_bounds__(TILE *TILE_ROWS) tile_kernel(const float *__re
     }
 }
 
+// ---- wide tile kernel: the same job with 64x64 tiles and 128-bit accesses ----------------------------
+// Used when sizes and strides allow float4 on every side (F and I sizes multiples of 4, 16-byte
+// aligned rows). 256 threads; a thread moves four float4 per operand and issues all of its global
+// loads before anything else. Transposed operands: float4 along F, scattered into padded shared
+// memory, read back along I. Direct operands: float4 along I (mode 1) or four scalars (mode 2,
+// broadcast or unaligned rows). Output: float4 along I. blockIdx.x walks the tiles of one batch
+// entry (I fastest), blockIdx.y the batch entries, whose index is split with multiply-high division.
+constexpr int WT = 64;
+template <int NOPS> struct WideTilePlan {
+    uint32_t nf, ni, tiles_i, batches;
+    uint64_t out_fstride;
+    int n_batch;                   // remaining dims, innermost first
+    Divider<uint32_t> batch[MAX_DIMS];
+    uint64_t out_bstride[MAX_DIMS];
+    uint64_t bstride[NOPS][MAX_DIMS];
+    uint64_t fstride[NOPS], istride[NOPS];
+    uint32_t mode[NOPS];           // 0: transposed through shared memory, 1: direct float4, 2: direct scalars
+};
+
+template <class Fn, int NOPS>
+__global__ void __launch_bounds__(256) wide_tile_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
+                                                        const __grid_constant__ WideTilePlan<NOPS> p, const LibmSplit split) {
+    __shared__ float sm[NOPS][WT][WT + 1];
+    const float *src[2] = {a, b};
+    const uint32_t ti = blockIdx.x % p.tiles_i, tf = blockIdx.x / p.tiles_i;
+    const uint32_t f0 = tf * WT, i0 = ti * WT;
+    const uint32_t q_hi = threadIdx.x >> 4, q_lo = (threadIdx.x & 15) * 4;  // (row 0..15, float4 column 0..60) of a 16-row slab
+    for (uint32_t bidx = blockIdx.y; bidx < p.batches; bidx += gridDim.y) {
+        uint64_t boff[NOPS], oboff = 0;
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) boff[o] = 0;
+        uint32_t rem = bidx;
+        for (int d = 0; d < p.n_batch; ++d) {
+            uint32_t q, r;
+            p.batch[d].divmod(rem, q, r);
+            rem = q;
+            oboff += (uint64_t)r * p.out_bstride[d];
+#pragma unroll
+            for (int o = 0; o < NOPS; ++o) boff[o] += (uint64_t)r * p.bstride[o][d];
+        }
+        float4 v[NOPS][4];
+        // Phase 1: every global load of this thread.
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t row = q_hi + 16 * k;  // 0..63
+                if (p.mode[o] == 0) {
+                    const uint32_t i = i0 + row, f = f0 + q_lo;  // 64 floats along F per I-row
+                    if (i < p.ni && f < p.nf) v[o][k] = ld4(src[o] + boff[o] + (uint64_t)i * p.istride[o] + f);
+                } else {
+                    const uint32_t f = f0 + row, i = i0 + q_lo;  // 64 floats along I per F-row
+                    if (f < p.nf && i < p.ni) {
+                        const float *q = src[o] + boff[o] + (uint64_t)f * p.fstride[o] + (uint64_t)i * p.istride[o];
+                        if (p.mode[o] == 1) v[o][k] = ld4(q);
+                        else v[o][k] = make_float4(q[0], q[p.istride[o]], q[2 * p.istride[o]], q[3 * p.istride[o]]);
+                    }
+                }
+            }
+        }
+        // Phase 2: transposed operands go through shared memory.
+#pragma unroll
+        for (int o = 0; o < NOPS; ++o) {
+            if (p.mode[o] == 0) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t il = q_hi + 16 * k;
+                    sm[o][q_lo + 0][il] = v[o][k].x;
+                    sm[o][q_lo + 1][il] = v[o][k].y;
+                    sm[o][q_lo + 2][il] = v[o][k].z;
+                    sm[o][q_lo + 3][il] = v[o][k].w;
+                }
+            }
+        }
+        __syncthreads();
+        // Phase 3: compute and store along I.
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t fl = q_hi + 16 * k, f = f0 + fl, i = i0 + q_lo;
+            if (f < p.nf && i < p.ni) {
+                float4 x[NOPS];
+#pragma unroll
+                for (int o = 0; o < NOPS; ++o)
+                    x[o] = p.mode[o] == 0 ? make_float4(sm[o][fl][q_lo], sm[o][fl][q_lo + 1], sm[o][fl][q_lo + 2], sm[o][fl][q_lo + 3]) : v[o][k];
+                const uint64_t pos = oboff + (uint64_t)f * p.out_fstride + i;
+                float4 r;
+                if constexpr (NOPS == 2) {
+                    r = make_float4(Fn::f(x[0].x, x[1].x), Fn::f(x[0].y, x[1].y), Fn::f(x[0].z, x[1].z), Fn::f(x[0].w, x[1].w));
+                } else {
+                    r = make_float4(apply_unary<Fn>(x[0].x, Fn::SPLIT && split.uses_libm(pos)), apply_unary<Fn>(x[0].y, Fn::SPLIT && split.uses_libm(pos + 1)),
+                                    apply_unary<Fn>(x[0].z, Fn::SPLIT && split.uses_libm(pos + 2)), apply_unary<Fn>(x[0].w, Fn::SPLIT && split.uses_libm(pos + 3)));
+                }
+                st4(out + pos, r);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---- generic gather kernel: any strides, one element per thread --------------------------------------
 template <int NOPS> struct GatherPlan {
     uint64_t n;
@@ -571,6 +670,55 @@ template <int NOPS> bool make_tile_plan(const EwProblem &p, TilePlan<NOPS> &t, u
     return ctas <= 0x7fffffffull;
 }
 
+// The wide tile kernel's plan, or false when sizes / strides do not allow 128-bit accesses throughout.
+template <int NOPS> bool make_wide_tile_plan(const EwProblem &p, WideTilePlan<NOPS> &t, dim3 &grid) {
+    if (p.nd < 2) return false;
+    int F = -1;
+    for (int o = 0; o < NOPS; ++o) {
+        if (p.dim[p.nd - 1].stride[o] <= 1) continue;
+        const int f = unit_stride_dim(p, o);
+        if (f < 0 || (F >= 0 && f != F)) return false;
+        F = f;
+    }
+    if (F < 0) return false;
+    const EwDim &df = p.dim[F], &di = p.dim[p.nd - 1];
+    if (df.size % 4 || di.size % 4 || df.size > UINT32_MAX || di.size > UINT32_MAX) return false;
+    t.nf = (uint32_t)df.size;
+    t.ni = (uint32_t)di.size;
+    const uint64_t tiles_f = (t.nf + WT - 1) / WT;
+    t.tiles_i = (t.ni + WT - 1) / WT;
+    if (tiles_f * t.tiles_i > 0x7fffffffull) return false;
+    uint64_t ostride[MAX_DIMS], acc = 1;
+    for (int d = p.nd - 1; d >= 0; --d) { ostride[d] = acc; acc *= p.dim[d].size; }
+    t.out_fstride = ostride[F];
+    t.n_batch = 0;
+    uint64_t batches = 1;
+    for (int d = p.nd - 2; d >= 0; --d) {
+        if (d == F) continue;
+        const int j = t.n_batch++;
+        t.batch[j] = Divider<uint32_t>(p.dim[d].size);
+        t.out_bstride[j] = ostride[d];
+        for (int o = 0; o < NOPS; ++o) t.bstride[o][j] = p.dim[d].stride[o];
+        batches *= p.dim[d].size;
+    }
+    if (batches > UINT32_MAX) return false;
+    t.batches = (uint32_t)batches;
+    for (int o = 0; o < NOPS; ++o) {
+        t.fstride[o] = df.stride[o];
+        t.istride[o] = di.stride[o];
+        bool aligned = true;  // every batch offset keeps 16-byte alignment
+        for (int j = 0; j < t.n_batch; ++j) aligned = aligned && t.bstride[o][j] % 4 == 0;
+        if (di.stride[o] > 1) {  // transposed: float4 along F at offset i*istride + f
+            if (!aligned || di.stride[o] % 4) return false;
+            t.mode[o] = 0;
+        } else {
+            t.mode[o] = (di.stride[o] == 1 && aligned && df.stride[o] % 4 == 0) ? 1 : 2;
+        }
+    }
+    grid = dim3((unsigned)(tiles_f * t.tiles_i), (unsigned)(batches < 65535 ? batches : 65535));
+    return true;
+}
+
 template <int NOPS> GatherPlan<NOPS> make_gather_plan(const EwProblem &p) {
     GatherPlan<NOPS> g{};
     g.n = p.n;
@@ -614,6 +762,12 @@ template <class Fn> cudaError_t run_binary(const float *a, const float *b, float
         }
         return cudaGetLastError();
     } else {
+        WideTilePlan<2> w{};
+        dim3 wgrid;
+        if (make_wide_tile_plan<2>(p, w, wgrid)) {
+            B200_LAUNCH((wide_tile_kernel<Fn, 2>), wgrid, 256, 0, s, a, b, out, w, LibmSplit{});
+            return cudaGetLastError();
+        }
         TilePlan<2> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<2>(p, t, ctas)) {
@@ -654,6 +808,12 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         return cudaGetLastError();
     }
     if (p.nd >= 2) {
+        WideTilePlan<1> w{};
+        dim3 wgrid;
+        if (make_wide_tile_plan<1>(p, w, wgrid)) {
+            B200_LAUNCH((wide_tile_kernel<Fn, 1>), wgrid, 256, 0, s, x, nullptr, out, w, split);
+            return cudaGetLastError();
+        }
         TilePlan<1> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<1>(p, t, ctas)) {

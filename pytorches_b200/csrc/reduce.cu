@@ -258,6 +258,79 @@ __global__ void __launch_bounds__(256) sum_cols_kernel(const float *__restrict__
     out[t] = s;
 }
 
+// inner > 1, staged: a CTA per group of 32 adjacent columns. Each column is still one ordered chain
+// (rows 0, 1, 2, ... added to 0.0), so the parallelism is fixed at outer*inner chains; what can be
+// decoupled is the loading. All 256 threads stream the group's [len x 32] slab into a ring of
+// COLS_DEPTH shared-memory stages with 16-byte cp.async (a 128-byte row segment is one full line,
+// 32 rows per instruction), and warp 0 alone walks the landed rows in order, lane = column. Needs
+// inner % 4 == 0 so that every 16-byte source address is aligned.
+constexpr int COLS_THREADS = 256;
+constexpr int COLS_STAGE_ROWS = 128;  // 128 rows x 128 B = 16 KiB per stage
+constexpr size_t cols_ring_bytes(int depth) { return (size_t)depth * COLS_STAGE_ROWS * 32 * sizeof(float); }
+// Ring depth: 4 stages (64 KiB, three CTAs per SM) when there are CTAs to spare, 12 stages (192 KiB,
+// the whole SM) when the column groups are fewer than two per SM and depth is the only source of
+// bytes in flight.
+constexpr int COLS_DEPTH_SHALLOW = 4, COLS_DEPTH_DEEP = 12;
+
+template <int COLS_DEPTH>
+__global__ void __launch_bounds__(COLS_THREADS) sum_cols_staged_kernel(const float *__restrict__ x, uint64_t len, uint64_t inner,
+                                                                       uint32_t groups_per_outer, float *__restrict__ out) {
+    extern __shared__ __align__(128) unsigned char cols_smem[];
+    float *ring = reinterpret_cast<float *>(cols_smem);  // [COLS_DEPTH][COLS_STAGE_ROWS][32]
+    const uint64_t o = blockIdx.x / groups_per_outer;
+    const uint32_t c0 = (blockIdx.x % groups_per_outer) * 32;
+    const uint32_t ncols = inner - c0 < 32 ? (uint32_t)(inner - c0) : 32;
+    const float *base = x + o * len * inner + c0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t seg = (threadIdx.x & 7) * 4, row_in = threadIdx.x >> 3;  // 8 threads cover one 128-byte row segment
+    const uint64_t stages = (len + COLS_STAGE_ROWS - 1) / COLS_STAGE_ROWS;
+    auto issue = [&](uint64_t st) {
+        float *dstp = ring + (size_t)(st % COLS_DEPTH) * COLS_STAGE_ROWS * 32;
+        if (seg < ncols) {
+#pragma unroll
+            for (int i = 0; i < COLS_STAGE_ROWS / 32; ++i) {
+                const uint64_t row = st * COLS_STAGE_ROWS + i * 32 + row_in;
+                if (row < len)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dstp + (i * 32 + row_in) * 32 + seg)),
+                                 "l"(base + row * inner + seg)
+                                 : "memory");
+            }
+        }
+    };
+    for (uint64_t st = 0; st < COLS_DEPTH - 1; ++st) {
+        if (st < stages) issue(st);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    float s = 0.0f;
+    for (uint64_t st = 0; st < stages; ++st) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(COLS_DEPTH - 2) : "memory");
+        __syncthreads();  // stage st has landed for everyone; warp 0 is done with stage st-1
+        if (st + COLS_DEPTH - 1 < stages) issue(st + COLS_DEPTH - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (warp == 0 && lane < (int)ncols) {
+            const float *buf = ring + (size_t)(st % COLS_DEPTH) * COLS_STAGE_ROWS * 32 + lane;
+            const uint32_t rows = (uint32_t)(len - st * COLS_STAGE_ROWS < COLS_STAGE_ROWS ? len - st * COLS_STAGE_ROWS : COLS_STAGE_ROWS);
+            // The chain costs one add latency per row; keep it there by fetching the next 32 rows from
+            // shared memory while the current 32 are added (reads past `rows` stay inside the ring).
+            const uint32_t full = rows & ~31u;
+            float cur[32], nxt[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) cur[u] = buf[u * 32];
+            for (uint32_t r = 0; r < full; r += 32) {
+                const uint32_t rn = r + 32 < COLS_STAGE_ROWS ? r + 32 : 0;
+#pragma unroll
+                for (int u = 0; u < 32; ++u) nxt[u] = buf[(rn + u) * 32];
+#pragma unroll
+                for (int u = 0; u < 32; ++u) s = __fadd_rn(s, cur[u]);
+#pragma unroll
+                for (int u = 0; u < 32; ++u) cur[u] = nxt[u];
+            }
+            for (uint32_t r = full; r < rows; ++r) s = __fadd_rn(s, buf[r * 32]);
+        }
+    }
+    if (warp == 0 && lane < (int)ncols) out[o * inner + c0 + lane] = s;
+}
+
 // ---- max / argmax ---------------------------------------------------------------------------------------
 
 // Should candidate (v, i) replace the current best (bv, bi)? NaN beats every number; among equals
@@ -490,15 +563,19 @@ int take_reduce_status() {
 }
 
 namespace {
-// Opts the TMA kernel into its 64 KiB of dynamic shared memory, once per device.
-bool tma_kernel_ready(int device) {
+// Opts the staged kernels into their 64 KiB of dynamic shared memory, once per device.
+bool staged_kernels_ready(int device) {
     static std::mutex mu;
     static bool done[64] = {}, ok[64] = {};
     if (device < 0 || device >= 64) return false;
     std::lock_guard<std::mutex> lock(mu);
     if (!done[device]) {
         done[device] = true;
-        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess;
+        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_cols_staged_kernel<COLS_DEPTH_SHALLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)cols_ring_bytes(COLS_DEPTH_SHALLOW)) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_cols_staged_kernel<COLS_DEPTH_DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)cols_ring_bytes(COLS_DEPTH_DEEP)) == cudaSuccess;
         if (!ok[device]) (void)cudaGetLastError();
     }
     return ok[device];
@@ -534,12 +611,27 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
             float *dst = blocks == 1 ? o : (float *)scratch;
             // Long rows whose block starts are 16-byte aligned take the TMA-staged kernel.
             int *status = (len >= 8 * TMA_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word() : nullptr;
-            if (status && tma_kernel_ready(device)) {
+            if (status && staged_kernels_ready(device)) {
                 B200_LAUNCH(sum_rows_tma_kernel, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status);
             } else {
                 B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
             }
             if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, COMBINE_THREADS, 0, s, (const float *)scratch, blocks, o);
+            return cudaGetLastError();
+        }
+        // Few, long columns: the staged kernel decouples loading from the ordered adds. Many columns
+        // already give the plain thread-per-column kernel enough loads in flight.
+        const uint64_t groups_per_outer = (inner + 31) / 32;
+        if (inner % 4 == 0 && inner >= 32 && len >= 128 && total < (1ull << 19) && outer * groups_per_outer <= 0x7fffffffull &&
+            staged_kernels_ready(device)) {
+            const unsigned ctas = (unsigned)(outer * groups_per_outer);
+            if (ctas < 2u * (unsigned)sm_count(device)) {
+                B200_LAUNCH(sum_cols_staged_kernel<COLS_DEPTH_DEEP>, ctas, COLS_THREADS, cols_ring_bytes(COLS_DEPTH_DEEP), s, x, len, inner,
+                            (uint32_t)groups_per_outer, o);
+            } else {
+                B200_LAUNCH(sum_cols_staged_kernel<COLS_DEPTH_SHALLOW>, ctas, COLS_THREADS, cols_ring_bytes(COLS_DEPTH_SHALLOW), s, x, len, inner,
+                            (uint32_t)groups_per_outer, o);
+            }
             return cudaGetLastError();
         }
         B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
