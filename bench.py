@@ -188,6 +188,12 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
 
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.
+    # Everything else goes to stderr: keep the real stdout aside for the final line.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch.distributed as dist
 
@@ -250,6 +256,7 @@ def main():
     l0 = launches()
     with ClockSampler(local) as clocks:
         ev[0].record(stream)
+        t_host = time.perf_counter()
         for k in range(args.steps):
             if world == 1:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -260,7 +267,9 @@ def main():
                 r = [s, x.mean(), x.max(), x.argmax()]
             else:
                 r = step(x)
+        group.flush()  # combines still deferred behind the last local pass
         ev[1].record(stream)
+        host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps  # time the host needs to ENQUEUE one step
         barrier()
     l1 = launches()
     ms = ev[0].elapsed_time(ev[1])
@@ -329,10 +338,11 @@ def main():
                    "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s), partials all-gathered over NCCL and combined by plugin ops" if world > 1 else "none",
                    "l2": "input (1 GiB) is larger than L2 (126 MB); no flush needed", "frac_of_measured_peak": round(value / (peak * world), 4),
                    "frac_of_8TBps": round(value / (8000.0 * world), 4)},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "roofline": roofline, "cpu_baseline": cpu,
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "roofline": roofline, "cpu_baseline": cpu,
         "ops_ms": {k: round(v, 5) for k, v in per_op.items()}, "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
     }
-    print(json.dumps(line))
+    sys.stdout.flush()
+    os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 

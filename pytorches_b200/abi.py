@@ -204,13 +204,21 @@ class Plugin:
         return bool(self.vt.supports_op(code))
 
     # ---- execute ----
-    @staticmethod
-    def _desc(a: Arg, keep: list) -> TensorDesc:
-        nd = len(a.shape)
-        sh = (C.c_uint64 * max(nd, 1))(*a.shape)
-        st = (C.c_uint64 * max(nd, 1))(*a.strides)
-        keep += [sh, st]
-        return TensorDesc(a.data, a.dtype, nd, sh, st)
+    _dims_cache: dict = {}
+
+    @classmethod
+    def _dims(cls, values: tuple):
+        """A ctypes u64 array for a shape or stride tuple (cached: the same few tuples recur on a hot path)."""
+        arr = cls._dims_cache.get(values)
+        if arr is None:
+            if len(cls._dims_cache) > 4096:
+                cls._dims_cache.clear()
+            arr = cls._dims_cache[values] = (C.c_uint64 * max(len(values), 1))(*values)
+        return arr
+
+    @classmethod
+    def _desc(cls, a: Arg, keep: list) -> TensorDesc:
+        return TensorDesc(a.data, a.dtype, len(a.shape), cls._dims(tuple(a.shape)), cls._dims(tuple(a.strides)))
 
     def execute_status(self, device: int, code: int, ints, inputs: list[Arg], outputs: list[Arg]) -> int:
         """Raw ``execute``: returns the status without raising (used by error-path tests)."""

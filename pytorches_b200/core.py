@@ -15,6 +15,7 @@ Not in the reference (appended ops 203/204): ``sum_dim``, ``max_dim``, ``argmax_
 from __future__ import annotations
 
 import ctypes as C
+import math
 import struct
 from typing import Callable, Optional, Sequence
 
@@ -129,7 +130,7 @@ def run_op_into(device: Device, code: int, ints, ins: list[Operand], out_buf: Bu
 
 def run_op(device: Device, code: int, ints, ins: list[Operand], out_shape, out_dtype=DTYPE_F32) -> "Tensor":
     """Allocate the output, then ``run_op_into`` (crates/core/src/lib.rs:331-335)."""
-    numel = int(np.prod(out_shape, dtype=np.int64)) if len(out_shape) else 1
+    numel = math.prod(out_shape)
     buf = Buffer(device, numel, 8 if out_dtype == DTYPE_I64 else 4)
     run_op_into(device, code, ints, ins, buf, out_shape, out_dtype)
     return Tensor(buf, out_shape, dtype=out_dtype)
@@ -178,7 +179,7 @@ class Tensor:
         return self.buffer.device
 
     def numel(self) -> int:
-        return int(np.prod(self.shape, dtype=np.int64)) if self.shape else 1
+        return math.prod(self.shape)
 
     def numpy(self) -> np.ndarray:
         """Blocking read-back (``to_vec``, lib.rs:507-515)."""
@@ -223,7 +224,7 @@ class Tensor:
         return self.raw_reduce_axis(op.SUM_AXIS, axis)
 
     def raw_reshape(self, shape) -> "Tensor":
-        if int(np.prod(shape, dtype=np.int64)) != self.numel():
+        if math.prod(shape) != self.numel():
             raise ValueError(f"cannot reshape {self.shape} to {list(shape)}")
         return Tensor(self.buffer, shape, dtype=self.dtype)
 

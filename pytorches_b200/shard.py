@@ -18,6 +18,7 @@ including the combine, is a plugin op on the device's in-order stream.
 from __future__ import annotations
 
 import ctypes as C
+import math
 from typing import Optional
 
 import numpy as np
@@ -25,7 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .abi import DTYPE_F32, DTYPE_I64, KIND_CUDA, Arg, contiguous_strides, op
-from .core import Buffer, Device, Operand, Tensor, run_op
+from .core import Buffer, Device, Operand, Tensor, run_op_into
 
 
 def split_rows(n: int, rank: int, world: int) -> tuple[int, int]:
@@ -55,6 +56,8 @@ class ShardGroup:
         self.device, self.rank, self.world, self.group = device, rank, world, group
         self.is_cuda = device.plugin.device_info(device.index).kind == KIND_CUDA
         self._stream = None
+        self._pending: list = []  # combines not yet enqueued: (collectives to wait for, what to enqueue)
+        self._views: dict = {}  # (pointer, elements, dtype) -> torch alias; the allocator hands the same blocks out again
         if self.is_cuda and world > 1:
             fn = device.plugin.lib.pytorches_b200_stream
             fn.restype, fn.argtypes = C.c_void_p, [C.c_uint32]
@@ -64,54 +67,139 @@ class ShardGroup:
     def torch_view(self, t: Tensor) -> torch.Tensor:
         """A torch tensor aliasing ``t``'s device memory, for handing to a collective."""
         n = t.numel()
-        if self.is_cuda:
-            typestr = "<i8" if t.dtype == DTYPE_I64 else "<f4"
-            return torch.as_tensor(_CudaView(t.buffer.ptr, (n,), typestr), device=torch.device("cuda", self.device.index))
-        ctype = C.c_int64 if t.dtype == DTYPE_I64 else C.c_float
-        return torch.from_numpy(np.ctypeslib.as_array((ctype * n).from_address(t.buffer.ptr)))
+        key = (t.buffer.ptr, n, t.dtype)
+        view = self._views.get(key)
+        if view is None:
+            if len(self._views) > 256:
+                self._views.clear()
+            if self.is_cuda:
+                typestr = "<i8" if t.dtype == DTYPE_I64 else "<f4"
+                view = torch.as_tensor(_CudaView(t.buffer.ptr, (n,), typestr), device=torch.device("cuda", self.device.index))
+            else:
+                ctype = C.c_int64 if t.dtype == DTYPE_I64 else C.c_float
+                view = torch.from_numpy(np.ctypeslib.as_array((ctype * n).from_address(t.buffer.ptr)))
+            self._views[key] = view
+        return view
 
-    def all_gather(self, t: Tensor) -> Tensor:
-        """[world, *t.shape]: row r holds rank r's ``t``. The collective is enqueued on the device's stream."""
-        out = Tensor(Buffer(self.device, self.world * t.numel(), 8 if t.dtype == DTYPE_I64 else 4), [self.world] + list(t.shape), dtype=t.dtype)
+    def _gather_async(self, t: Tensor):
+        """Starts the all-gather of ``t`` behind everything enqueued so far; returns (gathered tensor, work or None)."""
+        itemsize = 8 if t.dtype == DTYPE_I64 else 4
+        out = Tensor(Buffer(self.device, self.world * t.numel(), itemsize), [self.world] + list(t.shape), dtype=t.dtype)
         if self.world == 1:
-            self.device.plugin.copy_device_to_device(self.device.index, out.buffer.ptr, t.buffer.ptr, t.numel() * (8 if t.dtype == DTYPE_I64 else 4))
-            return out
+            self.device.plugin.copy_device_to_device(self.device.index, out.buffer.ptr, t.buffer.ptr, t.numel() * itemsize)
+            return out, None
         src, dst = self.torch_view(t), self.torch_view(out)
         if self._stream is not None:
             with torch.cuda.stream(self._stream):
-                dist.all_gather_into_tensor(dst, src, group=self.group)
+                work = dist.all_gather_into_tensor(dst, src, group=self.group, async_op=True)
         else:
-            dist.all_gather_into_tensor(dst, src, group=self.group)
+            work = dist.all_gather_into_tensor(dst, src, group=self.group, async_op=True)
+        return out, work
+
+    def _wait(self, work) -> None:
+        """Orders the device's stream (on CPU: the host) behind a collective started by ``_gather_async``."""
+        if work is None:
+            return
+        if self._stream is not None:
+            with torch.cuda.stream(self._stream):
+                work.wait()  # a stream-side wait; the host does not block
+        else:
+            work.wait()
+
+    def all_gather(self, t: Tensor) -> Tensor:
+        """[world, *t.shape]: row r holds rank r's ``t``. The collective is enqueued on the device's stream."""
+        out, work = self._gather_async(t)
+        self._wait(work)
         return out
 
+    # ---- deferred combines ----
+    # A sharded reduction is: local pass, exchange of the partials, combine. The exchange is latency, not
+    # bandwidth; to hide it, the combine of one reduction is enqueued only after the local pass of the
+    # NEXT one, so the collective runs (on the communication library's stream) beside that pass. Results
+    # are ``_Deferred`` tensors: touching their storage, or calling ``flush``, enqueues what is pending.
+    def flush(self) -> None:
+        pending, self._pending = self._pending, []
+        for works, finish in pending:
+            for w in works:
+                self._wait(w)
+            finish()
+
+    def _defer(self, local_pass, shape, dtype, finish_into) -> Tensor:
+        """``local_pass()`` -> list of partial tensors (enqueued now); ``finish_into(gathered, out_buffer)``
+        enqueues the combine later. Returns the tensor the combine will write."""
+        partials = local_pass()
+        self.flush()  # earlier reductions' collectives have had this local pass to hide behind
+        gathered, works = [], []
+        for part in partials:
+            g, w = self._gather_async(part)
+            gathered.append(g)
+            works.append(w)
+        out_buf = Buffer(self.device, math.prod(shape), 8 if dtype == DTYPE_I64 else 4)
+        keep = partials  # the collective reads them: keep them allocated until it has been waited for
+        self._pending.append((works, lambda: (finish_into(gathered, out_buf), keep.clear())))
+        return _Deferred(self, out_buf, shape, dtype)
+
     # ---- reductions that cross the sharded (leading) dimension ----
+    def _combine(self, code: int, out_dtype=DTYPE_F32):
+        def finish(gathered, out_buf):
+            g = gathered[0]
+            run_op_into(self.device, code, [0], [Operand.contiguous(g)], out_buf, g.shape[1:], out_dtype)
+        return finish
+
     def sum_axis0(self, x_local: Tensor) -> Tensor:
         """Sum over the sharded leading dimension: local SUM_AXIS(0), all-gather, SUM_AXIS(0) in rank order."""
-        return self.all_gather(x_local.raw_sum_axis(0)).raw_sum_axis(0)
+        return self._defer(lambda: [x_local.raw_sum_axis(0)], x_local.shape[1:], DTYPE_F32, self._combine(op.SUM_AXIS))
 
     def sum(self, x_local: Tensor) -> Tensor:
         """Full-tensor sum: every rank's ``Tensor.sum`` partial, combined in rank order."""
-        partial = x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)
-        return self.all_gather(partial).raw_sum_axis(0)
+        return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)], [], DTYPE_F32, self._combine(op.SUM_AXIS))
 
     def mean(self, x_local: Tensor, n_global: int) -> Tensor:
         """``Tensor.mean`` of the reference: the sum, then a DIV by the element count as a scalar tensor."""
-        return self.sum(x_local).raw_binary(Tensor.scalar_on(float(n_global), self.device), op.DIV)
+        def finish(gathered, out_buf):
+            total = gathered[0].raw_sum_axis(0)
+            count = Tensor.scalar_on(float(n_global), self.device)
+            run_op_into(self.device, op.DIV, [0], [Operand.contiguous(total), Operand.contiguous(count)], out_buf, [])
+        return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)], [], DTYPE_F32, finish)
 
     def max(self, x_local: Tensor) -> Tensor:
-        partial = x_local.raw_reshape([x_local.numel()]).raw_reduce_axis(op.MAX_AXIS, 0)
-        return self.all_gather(partial).raw_reduce_axis(op.MAX_AXIS, 0)
+        return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_reduce_axis(op.MAX_AXIS, 0)], [], DTYPE_F32,
+                           self._combine(op.MAX_AXIS))
 
     def argmax(self, x_local: Tensor, first_index: int) -> Tensor:
         """Position of the maximum in the unsharded flattened tensor; ``first_index`` is where this
         rank's shard starts in it. One pass yields (max, position); the pairs are gathered and the best
         is picked on every rank (NCCL has no pair reduction)."""
-        flat = x_local.raw_reshape([x_local.numel()])
-        val = Tensor(Buffer(self.device, 1), [])
-        idx = Tensor(Buffer(self.device, 1, 8), [], dtype=DTYPE_I64)
         dev = self.device
-        dev.plugin.execute(dev.index, op.MAX_ARGMAX_AXIS, [0, first_index],
-                           [Arg(flat.buffer.ptr, tuple(flat.shape), tuple(contiguous_strides(flat.shape)))],
-                           [Arg(val.buffer.ptr, (), ()), Arg(idx.buffer.ptr, (), (), DTYPE_I64)])
-        vals, idxs = self.all_gather(val), self.all_gather(idx)
-        return run_op(dev, op.ARGMAX_COMBINE, [0], [Operand.contiguous(vals), Operand.contiguous(idxs)], [], DTYPE_I64)
+
+        def local_pass():
+            flat = x_local.raw_reshape([x_local.numel()])
+            val = Tensor(Buffer(dev, 1), [])
+            idx = Tensor(Buffer(dev, 1, 8), [], dtype=DTYPE_I64)
+            dev.plugin.execute(dev.index, op.MAX_ARGMAX_AXIS, [0, first_index],
+                               [Arg(flat.buffer.ptr, tuple(flat.shape), tuple(contiguous_strides(flat.shape)))],
+                               [Arg(val.buffer.ptr, (), ()), Arg(idx.buffer.ptr, (), (), DTYPE_I64)])
+            return [val, idx]
+
+        def finish(gathered, out_buf):
+            run_op_into(dev, op.ARGMAX_COMBINE, [0], [Operand.contiguous(gathered[0]), Operand.contiguous(gathered[1])], out_buf, [], DTYPE_I64)
+
+        return self._defer(local_pass, [], DTYPE_I64, finish)
+
+
+class _Deferred(Tensor):
+    """Result of a sharded reduction whose combine may not have been enqueued yet. Reading its storage
+    (any op or read-back does) first enqueues everything its group has pending."""
+
+    def __init__(self, group: ShardGroup, buffer: Buffer, shape, dtype):
+        self._group, self._buf = group, buffer
+        super().__init__(buffer, shape, dtype=dtype)
+
+    @property
+    def buffer(self) -> Buffer:
+        self._group.flush()
+        return self._buf
+
+    @buffer.setter
+    def buffer(self, value: Buffer) -> None:
+        self._buf = value

@@ -26,7 +26,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, n: int):
+def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ["PYTORCHES_CPU_THREADS"] = "2"
@@ -35,11 +35,25 @@ def _worker(rank: int, world: int, port: int, n: int):
     from pytorches_b200.core import Device, Tensor
     from pytorches_b200.shard import ShardGroup, split_rows
 
-    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    if backend == "nccl":
+        import torch
+
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    else:
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
+        # Expected values always come from the CPU oracle; the sharded computation runs on the plugin
+        # under test (the oracle itself over gloo, the B200 plugin over NCCL: both must give the same bits).
         plugin = Plugin(ORACLE_SO)
         dev = Device(plugin, 0)
-        g = ShardGroup(dev, rank, world)
+        if backend == "nccl":
+            import pytorches_b200
+
+            gdev = Device(pytorches_b200.load_plugin(), rank)
+        else:
+            gdev = dev
+        g = ShardGroup(gdev, rank, world)
         bits = lambda a: np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
         # ---- full-tensor reductions over n elements, ties and a clear maximum in a late shard ----
@@ -48,7 +62,7 @@ def _worker(rank: int, world: int, port: int, n: int):
         x[n // 2] = 5.0  # the same maximum earlier: argmax must be the lower position, n // 2
         start, count = split_rows(n, rank, world)
         assert sum(split_rows(n, r, world)[1] for r in range(world)) == n
-        local = Tensor.from_numpy(x[start:start + count], dev)
+        local = Tensor.from_numpy(x[start:start + count], gdev)
         full = Tensor.from_numpy(x, dev)
 
         partials = []
@@ -77,7 +91,7 @@ def _worker(rank: int, world: int, port: int, n: int):
         b = lcg_data(cols, 2).reshape(1, cols)       # leading dim 1: replicated
         s_col = lcg_data(rows, 3).reshape(rows, 1)   # leading dim sharded like A
         r0, rc = split_rows(rows, rank, world)
-        out_local = (Tensor.from_numpy(A[r0:r0 + rc], dev) + Tensor.from_numpy(b, dev)).relu() * Tensor.from_numpy(s_col[r0:r0 + rc], dev)
+        out_local = (Tensor.from_numpy(A[r0:r0 + rc], gdev) + Tensor.from_numpy(b, gdev)).relu() * Tensor.from_numpy(s_col[r0:r0 + rc], gdev)
         out_full = (Tensor.from_numpy(A, dev) + Tensor.from_numpy(b, dev)).relu() * Tensor.from_numpy(s_col, dev)
         assert np.array_equal(bits(out_local.numpy()), bits(out_full.numpy()[r0:r0 + rc]))
         db = g.sum_axis0(out_local).numpy()
@@ -96,6 +110,15 @@ def _worker(rank: int, world: int, port: int, n: int):
 @pytest.mark.parametrize("world,n", [(2, 200_001), (3, 70_000)])
 def test_sharded_ops_over_gloo(oracle, world, n):
     mp.spawn(_worker, args=(world, _free_port(), n), nprocs=world, join=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,n", [(2, 200_001), (2, 1 << 22)])
+def test_sharded_ops_over_nccl(oracle, b200, world, n):
+    """The same checks with the B200 plugin on every rank and NCCL as the exchange (needs 2 GPUs)."""
+    if b200.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), n, "nccl"), nprocs=world, join=True)
 
 
 def test_split_rows_covers_everything():
