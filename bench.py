@@ -107,7 +107,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.002)
+            time.sleep(0.005)
 
     def __enter__(self):
         if self.nv:

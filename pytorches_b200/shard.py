@@ -62,6 +62,11 @@ class ShardGroup:
             fn = device.plugin.lib.pytorches_b200_stream
             fn.restype, fn.argtypes = C.c_void_p, [C.c_uint32]
             self._stream = torch.cuda.ExternalStream(fn(device.index), device=torch.device("cuda", device.index))
+            # Collectives order themselves against torch's CURRENT stream. A rank process of a sharded
+            # run has one job, so the plugin's stream is made current once, for good, instead of
+            # entering a stream context around every collective (that costs more host time per step
+            # than the collectives themselves).
+            torch.cuda.set_stream(self._stream)
 
     # ---- plumbing ----
     def torch_view(self, t: Tensor) -> torch.Tensor:
@@ -89,22 +94,12 @@ class ShardGroup:
             self.device.plugin.copy_device_to_device(self.device.index, out.buffer.ptr, t.buffer.ptr, t.numel() * itemsize)
             return out, None
         src, dst = self.torch_view(t), self.torch_view(out)
-        if self._stream is not None:
-            with torch.cuda.stream(self._stream):
-                work = dist.all_gather_into_tensor(dst, src, group=self.group, async_op=True)
-        else:
-            work = dist.all_gather_into_tensor(dst, src, group=self.group, async_op=True)
-        return out, work
+        return out, dist.all_gather_into_tensor(dst, src, group=self.group, async_op=True)
 
     def _wait(self, work) -> None:
         """Orders the device's stream (on CPU: the host) behind a collective started by ``_gather_async``."""
-        if work is None:
-            return
-        if self._stream is not None:
-            with torch.cuda.stream(self._stream):
-                work.wait()  # a stream-side wait; the host does not block
-        else:
-            work.wait()
+        if work is not None:
+            work.wait()  # on a GPU this is a stream-side wait: the host does not block
 
     def all_gather(self, t: Tensor) -> Tensor:
         """[world, *t.shape]: row r holds rank r's ``t``. The collective is enqueued on the device's stream."""
