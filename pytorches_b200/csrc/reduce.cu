@@ -18,6 +18,8 @@
 #include <cstdio>
 #include <mutex>
 
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up at run time, libcuda is not linked
+
 #include "common.cuh"
 
 namespace b200 {
@@ -258,77 +260,92 @@ __global__ void __launch_bounds__(256) sum_cols_kernel(const float *__restrict__
     out[t] = s;
 }
 
-// inner > 1, staged: a CTA per group of 32 adjacent columns. Each column is still one ordered chain
-// (rows 0, 1, 2, ... added to 0.0), so the parallelism is fixed at outer*inner chains; what can be
-// decoupled is the loading. All 256 threads stream the group's [len x 32] slab into a ring of
-// COLS_DEPTH shared-memory stages with 16-byte cp.async (a 128-byte row segment is one full line,
-// 32 rows per instruction), and warp 0 alone walks the landed rows in order, lane = column. Needs
-// inner % 4 == 0 so that every 16-byte source address is aligned.
-constexpr int COLS_THREADS = 256;
-constexpr int COLS_STAGE_ROWS = 128;  // 128 rows x 128 B = 16 KiB per stage
-constexpr size_t cols_ring_bytes(int depth) { return (size_t)depth * COLS_STAGE_ROWS * 32 * sizeof(float); }
-// Ring depth: 4 stages (64 KiB, three CTAs per SM) when there are CTAs to spare, 12 stages (192 KiB,
-// the whole SM) when the column groups are fewer than two per SM and depth is the only source of
-// bytes in flight.
-constexpr int COLS_DEPTH_SHALLOW = 4, COLS_DEPTH_DEEP = 12;
+// inner > 1, TMA-staged: a one-warp CTA per group of 32 adjacent columns. Each column is still one
+// ordered chain (rows 0, 1, 2, ... added to 0.0), so the parallelism is fixed at outer*inner chains and
+// a chain advances one add latency per row; what can be taken off the warp is the loading. The
+// [outer*len, inner] input is described to the TMA engine as a 2-D tensor; lane 0 keeps COLS_STAGES
+// tile copies of [128 rows x 32 columns] (16 KiB) in flight into a shared-memory ring, each completing
+// on an mbarrier, and the warp walks a landed tile row by row, lane = column (conflict-free). No other
+// warps, no CTA barriers. Tiles that reach past the tensor (or past `inner`) are zero-filled by the
+// hardware and those rows / columns are simply not consumed. Waits are bounded as in the row kernel.
+// Tile height: 128 rows (16 KiB tiles, 64 KiB ring, three CTAs per SM) when there are CTAs to spare;
+// 256 rows (the TMA box limit; 128 KiB ring) when the column groups are fewer than two per SM, which
+// halves the per-tile bookkeeping of the one warp that does everything.
+constexpr int COLS_STAGES = 4;
+constexpr size_t cols_smem(int tile_rows) { return (size_t)COLS_STAGES * tile_rows * 128 + 8 * 128; }  // + 8 rows of slack for look-ahead loads
 
-template <int COLS_DEPTH>
-__global__ void __launch_bounds__(COLS_THREADS) sum_cols_staged_kernel(const float *__restrict__ x, uint64_t len, uint64_t inner,
-                                                                       uint32_t groups_per_outer, float *__restrict__ out) {
-    extern __shared__ __align__(128) unsigned char cols_smem[];
-    float *ring = reinterpret_cast<float *>(cols_smem);  // [COLS_DEPTH][COLS_STAGE_ROWS][32]
+__device__ __forceinline__ void tile_load_2d(void *dst, const CUtensorMap *map, int32_t x, int32_t y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_addr(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+template <int COLS_TILE_ROWS>
+__global__ void __launch_bounds__(32) sum_cols_tma_kernel(const __grid_constant__ CUtensorMap map, uint64_t len, uint64_t inner,
+                                                          uint32_t groups_per_outer, float *__restrict__ out, int *status) {
+    constexpr uint32_t COLS_TILE_BYTES = COLS_TILE_ROWS * 32 * sizeof(float);
+    extern __shared__ __align__(128) unsigned char cols_ring[];
+    __shared__ uint64_t bars[COLS_STAGES];
+    float *ring = reinterpret_cast<float *>(cols_ring);  // [COLS_STAGES][COLS_TILE_ROWS][32]
+    const int lane = threadIdx.x;
+    if (lane == 0) {
+        for (int s = 0; s < COLS_STAGES; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
     const uint64_t o = blockIdx.x / groups_per_outer;
     const uint32_t c0 = (blockIdx.x % groups_per_outer) * 32;
     const uint32_t ncols = inner - c0 < 32 ? (uint32_t)(inner - c0) : 32;
-    const float *base = x + o * len * inner + c0;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t seg = (threadIdx.x & 7) * 4, row_in = threadIdx.x >> 3;  // 8 threads cover one 128-byte row segment
-    const uint64_t stages = (len + COLS_STAGE_ROWS - 1) / COLS_STAGE_ROWS;
-    auto issue = [&](uint64_t st) {
-        float *dstp = ring + (size_t)(st % COLS_DEPTH) * COLS_STAGE_ROWS * 32;
-        if (seg < ncols) {
-#pragma unroll
-            for (int i = 0; i < COLS_STAGE_ROWS / 32; ++i) {
-                const uint64_t row = st * COLS_STAGE_ROWS + i * 32 + row_in;
-                if (row < len)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dstp + (i * 32 + row_in) * 32 + seg)),
-                                 "l"(base + row * inner + seg)
-                                 : "memory");
-            }
+    const uint64_t row0 = o * len;  // first row of this slab in the 2-D view
+    const uint32_t tiles = (uint32_t)((len + COLS_TILE_ROWS - 1) / COLS_TILE_ROWS);
+    if (lane == 0) {
+        for (uint32_t t = 0; t < COLS_STAGES && t < tiles; ++t) {
+            mbar_expect_tx(&bars[t], COLS_TILE_BYTES);
+            tile_load_2d(ring + (size_t)t * COLS_TILE_ROWS * 32, &map, (int32_t)c0, (int32_t)(row0 + (uint64_t)t * COLS_TILE_ROWS), &bars[t]);
         }
-    };
-    for (uint64_t st = 0; st < COLS_DEPTH - 1; ++st) {
-        if (st < stages) issue(st);
-        asm volatile("cp.async.commit_group;" ::: "memory");
     }
     float s = 0.0f;
-    for (uint64_t st = 0; st < stages; ++st) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(COLS_DEPTH - 2) : "memory");
-        __syncthreads();  // stage st has landed for everyone; warp 0 is done with stage st-1
-        if (st + COLS_DEPTH - 1 < stages) issue(st + COLS_DEPTH - 1);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (warp == 0 && lane < (int)ncols) {
-            const float *buf = ring + (size_t)(st % COLS_DEPTH) * COLS_STAGE_ROWS * 32 + lane;
-            const uint32_t rows = (uint32_t)(len - st * COLS_STAGE_ROWS < COLS_STAGE_ROWS ? len - st * COLS_STAGE_ROWS : COLS_STAGE_ROWS);
-            // The chain costs one add latency per row; keep it there by fetching the next 32 rows from
-            // shared memory while the current 32 are added (reads past `rows` stay inside the ring).
-            const uint32_t full = rows & ~31u;
-            float cur[32], nxt[32];
-#pragma unroll
-            for (int u = 0; u < 32; ++u) cur[u] = buf[u * 32];
-            for (uint32_t r = 0; r < full; r += 32) {
-                const uint32_t rn = r + 32 < COLS_STAGE_ROWS ? r + 32 : 0;
-#pragma unroll
-                for (int u = 0; u < 32; ++u) nxt[u] = buf[(rn + u) * 32];
-#pragma unroll
-                for (int u = 0; u < 32; ++u) s = __fadd_rn(s, cur[u]);
-#pragma unroll
-                for (int u = 0; u < 32; ++u) cur[u] = nxt[u];
+    for (uint32_t t = 0; t < tiles; ++t) {
+        const int st = t % COLS_STAGES;
+        if (!mbar_wait_bounded(&bars[st], (t / COLS_STAGES) & 1)) {
+            for (uint32_t d = t + 1; d < tiles && d < t + COLS_STAGES; ++d) (void)mbar_wait_bounded(&bars[d % COLS_STAGES], (d / COLS_STAGES) & 1);
+            if (lane == 0) {
+                *(volatile int *)status = STATUS_WAIT_EXPIRED;
+                __threadfence_system();
             }
-            for (uint32_t r = full; r < rows; ++r) s = __fadd_rn(s, buf[r * 32]);
+            return;
+        }
+        const float *buf = ring + (size_t)st * COLS_TILE_ROWS * 32 + lane;
+        const uint32_t rows = (uint32_t)(len - (uint64_t)t * COLS_TILE_ROWS < COLS_TILE_ROWS ? len - (uint64_t)t * COLS_TILE_ROWS : COLS_TILE_ROWS);
+        // One warp, one dependent add per row: the loop must cost little more than the add latency.
+        // The shared-memory load of row r+8 is issued between the adds of rows r and r+1 (volatile asm
+        // pins that order), so loads ride in the adds' latency shadow instead of running in batches.
+        uint32_t r = 0;
+        if (rows >= 32) {
+            const uint32_t addr = smem_addr(buf);
+            float v[40];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[u]) : "r"(addr + u * 128));
+            for (; r + 32 <= rows; r += 32) {
+                const uint32_t a = addr + r * 128;
+#pragma unroll
+                for (int u = 0; u < 32; ++u) {
+                    // rows past the tile's end are never added; the address stays inside the ring
+                    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[(u + 8) % 40]) : "r"(a + (u + 8) * 128));
+                    s = __fadd_rn(s, v[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = v[32 + u];
+            }
+        }
+        for (; r < rows; ++r) s = __fadd_rn(s, buf[r * 32]);
+        __syncwarp();  // every lane is done with this stage before it is refilled
+        if (lane == 0 && t + COLS_STAGES < tiles) {
+            mbar_expect_tx(&bars[st], COLS_TILE_BYTES);
+            tile_load_2d(ring + (size_t)st * COLS_TILE_ROWS * 32, &map, (int32_t)c0, (int32_t)(row0 + (uint64_t)(t + COLS_STAGES) * COLS_TILE_ROWS), &bars[st]);
         }
     }
-    if (warp == 0 && lane < (int)ncols) out[o * inner + c0 + lane] = s;
+    if (lane < (int)ncols) out[o * inner + c0 + lane] = s;
 }
 
 // ---- max / argmax ---------------------------------------------------------------------------------------
@@ -572,13 +589,37 @@ bool staged_kernels_ready(int device) {
     if (!done[device]) {
         done[device] = true;
         ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
-                     cudaFuncSetAttribute(sum_cols_staged_kernel<COLS_DEPTH_SHALLOW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)cols_ring_bytes(COLS_DEPTH_SHALLOW)) == cudaSuccess &&
-                     cudaFuncSetAttribute(sum_cols_staged_kernel<COLS_DEPTH_DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          (int)cols_ring_bytes(COLS_DEPTH_DEEP)) == cudaSuccess;
+                     cudaFuncSetAttribute(sum_cols_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(128)) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_cols_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(256)) == cudaSuccess;
         if (!ok[device]) (void)cudaGetLastError();
     }
     return ok[device];
+}
+
+// Describes x, viewed as a row-major [rows, inner] f32 matrix, to the TMA engine with tiles of
+// [COLS_TILE_ROWS x 32]. The encoder lives in the driver; it is looked up through the runtime so that
+// this library still has no link-time dependency on libcuda. False if it is unavailable or refuses.
+// Tiles are [tile_rows x 32].
+bool make_cols_tensor_map(CUtensorMap *map, const float *x, uint64_t rows, uint64_t inner, uint32_t tile_rows) {
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            fn = nullptr;
+        }
+        return (EncodeFn)fn;
+    }();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {inner * sizeof(float)};
+    const cuuint32_t box[2] = {32, tile_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)x, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 }  // namespace
 
@@ -619,20 +660,21 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
             if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, COMBINE_THREADS, 0, s, (const float *)scratch, blocks, o);
             return cudaGetLastError();
         }
-        // Few, long columns: the staged kernel decouples loading from the ordered adds. Many columns
-        // already give the plain thread-per-column kernel enough loads in flight.
+        // Few, long columns: the TMA-staged kernel takes the loading off the ordered chains. Many
+        // columns already give the plain thread-per-column kernel enough loads in flight. The tile
+        // coordinates are 32-bit and the row pitch must be a multiple of 16 bytes.
         const uint64_t groups_per_outer = (inner + 31) / 32;
-        if (inner % 4 == 0 && inner >= 32 && len >= 128 && total < (1ull << 19) && outer * groups_per_outer <= 0x7fffffffull &&
-            staged_kernels_ready(device)) {
+        if (inner % 4 == 0 && inner >= 32 && len >= 128 && total < (1ull << 19) && outer * len < 0x7fffffffull &&
+            outer * groups_per_outer <= 0x7fffffffull && staged_kernels_ready(device)) {
+            CUtensorMap map;
+            int *status = reduce_status_word();
             const unsigned ctas = (unsigned)(outer * groups_per_outer);
-            if (ctas < 2u * (unsigned)sm_count(device)) {
-                B200_LAUNCH(sum_cols_staged_kernel<COLS_DEPTH_DEEP>, ctas, COLS_THREADS, cols_ring_bytes(COLS_DEPTH_DEEP), s, x, len, inner,
-                            (uint32_t)groups_per_outer, o);
-            } else {
-                B200_LAUNCH(sum_cols_staged_kernel<COLS_DEPTH_SHALLOW>, ctas, COLS_THREADS, cols_ring_bytes(COLS_DEPTH_SHALLOW), s, x, len, inner,
-                            (uint32_t)groups_per_outer, o);
+            const bool tall = ctas < 2u * (unsigned)sm_count(device) && len >= 1024;
+            if (status && make_cols_tensor_map(&map, x, outer * len, inner, tall ? 256 : 128)) {
+                if (tall) B200_LAUNCH(sum_cols_tma_kernel<256>, ctas, 32, cols_smem(256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                else B200_LAUNCH(sum_cols_tma_kernel<128>, ctas, 32, cols_smem(128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                return cudaGetLastError();
             }
-            return cudaGetLastError();
         }
         B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
         return cudaGetLastError();
