@@ -62,6 +62,18 @@ uint64_t pytorches_b200_kernel_launches(void);
  */
 int32_t pytorches_b200_sum_noalloc(uint32_t device, const float *x, uint64_t n, float *out, void *stream);
 
+/*
+ * Failure-path self test. The staged reduction kernels wait for their asynchronous copies with a
+ * bounded number of tries; if a wait ever ran out they would record it in a host-visible status word
+ * and the next blocking vtable call (synchronize, copy_to_host) would return PT_STATUS_INTERNAL
+ * instead of a wrong result (docs/plugin-abi.md:155-156, deferred failures). This entry point enqueues,
+ * on `stream`, a tiny kernel whose wait is certain to run out (it waits for bytes nobody sends, for a
+ * few thousand tries: milliseconds) and that reports it through the same word. The GPU neither hangs
+ * nor faults. After it, exactly one blocking call on that device reports the error; later calls work.
+ * Replaces nothing in the reference. Returns a PtStatus for the enqueue itself.
+ */
+int32_t pytorches_b200_selftest_expired_wait(uint32_t device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

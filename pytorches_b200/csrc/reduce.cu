@@ -815,3 +815,49 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noa
     }
 }
 
+// ---- exercising the expired-wait path without a fault --------------------------------------------------
+// A one-warp kernel arms an mbarrier for bytes that no copy will ever deliver, waits for it with a
+// small limit, and reports the expiry exactly as the staged reduction kernels would. Nothing hangs and
+// nothing faults: the wait simply runs out. Lets a host (and the test suite) check that an expired
+// device-side wait surfaces as an error from the next blocking call and that the device stays usable.
+namespace b200 {
+namespace {
+__global__ void __launch_bounds__(32) expired_wait_kernel(int *status, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(&bar, 16);  // nobody sends these 16 bytes
+    }
+    __syncwarp();
+    bool done = false;
+    for (uint32_t tries = 0; tries < limit && !done; ++tries) done = mbar_try_wait(&bar, 0);
+    if (!done && threadIdx.x == 0) {
+        *(volatile int *)status = STATUS_WAIT_EXPIRED;
+        __threadfence_system();
+    }
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_selftest_expired_wait(uint32_t device, void *stream) {
+    using namespace b200;
+    try {
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || (int)device >= count) {
+            (void)cudaGetLastError();
+            set_last_error("b200: selftest_expired_wait: no such device");
+            return 3;
+        }
+        int *status = reduce_status_word();
+        if (!status || cudaSetDevice((int)device) != cudaSuccess) {
+            (void)cudaGetLastError();
+            set_last_error("b200: selftest_expired_wait: set-up failed");
+            return 4;
+        }
+        B200_LAUNCH(expired_wait_kernel, 1, 32, 0, (cudaStream_t)stream, status, 2000u);
+        return cudaGetLastError() == cudaSuccess ? 0 : 4;
+    } catch (...) {
+        return 4;
+    }
+}
