@@ -314,3 +314,63 @@ def test_config2_full_reductions(oracle, b200):
     assert got[3] == want[3]
     ref = x0.astype(np.float64).sum()
     assert abs(float(got[0]) - ref) <= 1e-5 * 22 * np.abs(x0.astype(np.float64)).sum()
+
+
+# ---- the same configurations at the benchmark's FULL sizes ----------------------------------------------
+# The oracle finishes these in about a second each, so they are compared bit for bit as well.
+
+def test_config1_full_size_bit_exact(oracle, b200):
+    m = n = 4096
+    cpu = Device(oracle, 0)
+    A0, b0, s0 = (Tensor.randn_on(sh, seed, cpu).numpy() for sh, seed in (([m, n], 1), ([1, n], 2), ([m, 1], 3)))
+
+    def step(dev):
+        A, b, s = (Tensor.from_numpy(v, dev, True) for v in (A0, b0, s0))
+        out = (A + b).relu() * s
+        r = out.sum_dim(1)
+        out.sum().backward()
+        return [r, A.grad, b.grad, s.grad]
+
+    got, want = run_on(b200, step), run_on(oracle, step)
+    for name, g, w in zip(["r", "dA", "db", "ds"], got, want):
+        assert_bit_equal(f"config 1 full size {name}", g, w, zero_sign_matters=False)
+
+
+def test_config4_full_size_bit_exact(oracle, b200):
+    if b200.device_info(0).free_memory < 24 * (1 << 30):
+        pytest.skip("needs 24 GiB of free device memory")
+    B, R, Cn = 64, 2048, 2048
+    cpu = Device(oracle, 0)
+    X0 = Tensor.randn_on([B, R, Cn], 21, cpu).numpy() * np.float32(2.0)
+    m10 = Tensor.randn_on([B, 1, Cn], 22, cpu).numpy()
+    m20 = np.where(lcg_data(R, 23) < -0.8, np.float32(-1e4), np.float32(0.0)).astype(np.float32).reshape(1, R, 1)
+
+    def step(dev):
+        Y = Tensor.from_numpy(X0, dev) + Tensor.from_numpy(m10, dev) + Tensor.from_numpy(m20, dev)
+        M = Y.max_dim(2, keepdim=True)
+        E = (Y - M).exp()
+        del Y
+        S = E.sum_dim(2, keepdim=True)
+        P = E / S
+        del E
+        return [M, S, P]
+
+    got = run_on(b200, step)
+    want = run_on(oracle, step)
+    for name, g, w in zip(["M", "S", "P"], got, want):
+        assert_bit_equal(f"config 4 full size {name}", g, w)
+
+
+def test_config2_full_size_against_oracle(oracle, b200):
+    """2^28 elements: sum and mean bit-equal to the oracle's, max and argmax exact."""
+    x0 = Tensor.randn_on([1 << 28], 7, Device(oracle, 0)).numpy()
+
+    def step(dev):
+        x = Tensor.from_numpy(x0, dev)
+        return [x.sum(), x.mean(), x.max(), x.argmax()]
+
+    got, want = run_on(b200, step), run_on(oracle, step)
+    for name, g, w in zip(["sum", "mean", "max"], got, want):
+        assert_bit_equal(f"config 2 full size {name}", g, w)
+    assert got[3] == want[3]
+
