@@ -121,12 +121,81 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                  : "memory");
 }
 
+// FUSED (one row only): the ordered chain over the block sums runs INSIDE this launch. CTA 0 is the
+// combiner; CTAs 1..blocks are the workers. A worker publishes its block sum as ONE 64-bit word,
+// (epoch << 32) | float bits, into a per-device mailbox; the combiner polls the words in block order
+// (the mailbox persists between launches and every launch has a new epoch, so a word of this launch
+// cannot be mistaken for an old one and nothing needs clearing), adds each sum as soon as it is there
+// and writes the result. With 4096 workers taking three CTA slots per SM at a time, block sums arrive
+// in waves and the chain hides behind the streaming; only the last wave's sums are added after it.
+// A 64-bit aligned store is indivisible, so no fence and no atomic is needed, and the order of the
+// adds (hence the bits) is the reference's. The combiner's polls are bounded like every other wait.
+constexpr uint32_t POLL_LIMIT = 1u << 21;
+
+__device__ __forceinline__ unsigned long long ld_mailbox(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 256 words
+// per round (8 per lane, all in flight together) and re-polls only the ones not yet published.
+constexpr int COMBINER_WORDS = 8;
+
+__device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status) {
+    const int lane = threadIdx.x;
+    float s = 0.0f;
+    for (uint64_t base = 0; base < blocks; base += 32 * COMBINER_WORDS) {
+        float v[COMBINER_WORDS];
+        uint32_t missing = 0;
+#pragma unroll
+        for (int k = 0; k < COMBINER_WORDS; ++k) {
+            v[k] = 0.0f;
+            if (base + k * 32 + lane < blocks) missing |= 1u << k;
+        }
+        for (uint32_t tries = 0; tries < POLL_LIMIT && __any_sync(0xffffffffu, missing != 0); ++tries) {
+            unsigned long long w[COMBINER_WORDS];
+#pragma unroll
+            for (int k = 0; k < COMBINER_WORDS; ++k)
+                if (missing & (1u << k)) w[k] = ld_mailbox(mailbox + base + k * 32 + lane);
+#pragma unroll
+            for (int k = 0; k < COMBINER_WORDS; ++k)
+                if ((missing & (1u << k)) && (uint32_t)(w[k] >> 32) == epoch) {
+                    v[k] = __uint_as_float((uint32_t)w[k]);
+                    missing &= ~(1u << k);
+                }
+        }
+        if (__any_sync(0xffffffffu, missing != 0)) {
+            if (lane == 0) {
+                *(volatile int *)status = STATUS_WAIT_EXPIRED;
+                __threadfence_system();
+            }
+            return;
+        }
+        // Every lane runs the same chain; the sums are broadcast by shuffles, which are off the chain.
+#pragma unroll
+        for (int k = 0; k < COMBINER_WORDS; ++k) {
+            const uint64_t first = base + (uint64_t)k * 32;
+            if (first >= blocks) break;
+            if (blocks - first >= 32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v[k], j));
+            } else {
+                for (int j = 0; j < (int)(blocks - first); ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v[k], j));
+            }
+        }
+    }
+    if (lane == 0) out[0] = s;
+}
+
+template <bool FUSED>
 __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
-                                                          float *__restrict__ dst, int *status) {
+                                                          float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch) {
     extern __shared__ __align__(128) unsigned char tma_smem[];
     __shared__ uint64_t bars[TMA_STAGES];
     float *ring = reinterpret_cast<float *>(tma_smem);
-    const uint64_t t = blockIdx.x;
+    if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status);
+    const uint64_t t = FUSED ? blockIdx.x - 1 : blockIdx.x;
     const int lane = threadIdx.x;
     if (lane == 0) {
         for (int s = 0; s < TMA_STAGES; ++s) mbar_init(&bars[s], 1);
@@ -181,7 +250,12 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
     s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 1));
     if (lane == 0) {
         for (uint32_t i = m32; i < m; ++i) s = __fadd_rn(s, p[i]);
-        dst[t] = blocks == 1 ? __fadd_rn(0.0f, s) : s;
+        if (FUSED) {
+            const unsigned long long w = ((unsigned long long)epoch << 32) | __float_as_uint(s);
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(mailbox + t), "l"(w) : "memory");
+        } else {
+            dst[t] = blocks == 1 ? __fadd_rn(0.0f, s) : s;
+        }
     }
 }
 
@@ -580,6 +654,36 @@ int take_reduce_status() {
 }
 
 namespace {
+// The fused sum's mailbox: MAILBOX_SLOTS 64-bit words per device, allocated and zeroed on first use,
+// kept for the life of the process. Each launch gets the next epoch (never 0); when the 32-bit epoch
+// wraps the words are zeroed again, on the stream, so no stale word can match.
+constexpr uint64_t MAILBOX_SLOTS = 1ull << 20;  // one per 65536 elements: rows of up to 2^36 elements
+unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
+    static std::mutex mu;
+    static unsigned long long *box[64] = {};
+    static uint32_t next[64] = {};
+    if (device < 0 || device >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!box[device]) {
+        void *p = nullptr;
+        if (cudaMalloc(&p, MAILBOX_SLOTS * 8) != cudaSuccess || cudaMemsetAsync(p, 0, MAILBOX_SLOTS * 8, s) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (p) (void)cudaFree(p);
+            return nullptr;
+        }
+        box[device] = (unsigned long long *)p;
+    }
+    if (++next[device] == 0) {
+        if (cudaMemsetAsync(box[device], 0, MAILBOX_SLOTS * 8, s) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        next[device] = 1;
+    }
+    *epoch = next[device];
+    return box[device];
+}
+
 // Opts the staged kernels into their 64 KiB of dynamic shared memory, once per device.
 bool staged_kernels_ready(int device) {
     static std::mutex mu;
@@ -588,7 +692,8 @@ bool staged_kernels_ready(int device) {
     std::lock_guard<std::mutex> lock(mu);
     if (!done[device]) {
         done[device] = true;
-        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
+        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_rows_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
                      cudaFuncSetAttribute(sum_cols_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(128)) == cudaSuccess &&
                      cudaFuncSetAttribute(sum_cols_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(256)) == cudaSuccess;
         if (!ok[device]) (void)cudaGetLastError();
@@ -653,7 +758,15 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
             // Long rows whose block starts are 16-byte aligned take the TMA-staged kernel.
             int *status = (len >= 8 * TMA_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word() : nullptr;
             if (status && staged_kernels_ready(device)) {
-                B200_LAUNCH(sum_rows_tma_kernel, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status);
+                // A single long row: chain the block sums inside the same launch (see ordered_combiner).
+                uint32_t epoch = 0;
+                unsigned long long *mailbox = (outer == 1 && blocks >= 64 && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
+                if (mailbox) {
+                    B200_LAUNCH(sum_rows_tma_kernel<true>, (unsigned)tasks + 1, 32, TMA_SMEM, s, x, tasks, len, blocks, o, status, mailbox, epoch);
+                    return cudaGetLastError();
+                }
+                B200_LAUNCH(sum_rows_tma_kernel<false>, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status,
+                            (unsigned long long *)nullptr, 0u);
             } else {
                 B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
             }

@@ -9,6 +9,10 @@ fill (the reference's accounting, benchmarks/bench.py:166-170). Inputs are large
 Usage:
   python -m pytorches_b200.opbench --op add --elements 268435456 --iters 20
   python -m pytorches_b200.opbench --sweep            # 1 MiB .. 4 GiB, powers of 4, all ops
+  python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m pytorches_b200.opbench --op add,sum ...
+Under torch.distributed.run every rank runs the op on its own shard of --elements elements PER GPU
+(dim-0 sharding, weak scaling); elementwise ops need no exchange, full-tensor reductions end with the
+shard layer's combine; the line reports the aggregate over all GPUs with the slowest rank's time.
 Ops: add mul div (contiguous), add_row (x[N/1024,1024] + b[1,1024]), add_col (x[R,1024] + s[R,1]),
 exp relu neg, sum mean max argmax (full tensor), sum_rows max_rows (rows of 2048), sum_cols, axpy, fill,
 add_t (transposed operand).
@@ -32,8 +36,9 @@ OPS = ["add", "mul", "div", "add_row", "add_col", "add_t", "exp", "relu", "neg",
        "sum", "mean", "max", "argmax", "sum_rows", "max_rows", "sum_cols"]
 
 
-def build_case(name: str, n: int, dev: Device):
-    """Returns (callable issuing the op once, algorithmic bytes)."""
+def build_case(name: str, n: int, dev: Device, group=None):
+    """Returns (callable issuing the op once, algorithmic bytes). ``group``: a ShardGroup when several
+    ranks each hold a shard of n elements; full-tensor reductions then include the cross-GPU combine."""
     uni = lambda shape, seed: Tensor.randn_on(shape, seed, dev)
     if name in ("add", "mul", "div"):
         a, b = uni([n], 31), uni([n], 32).exp()  # second operand positive: a safe divisor
@@ -62,7 +67,17 @@ def build_case(name: str, n: int, dev: Device):
         out = uni([n], 31)
         return (lambda: run_op_into(dev, op.FILL, [0x3F800000], [], out.buffer, [n])), 4 * n
     if name in ("sum", "mean", "max", "argmax"):
-        a = uni([n], 31)
+        a = uni([n], 31 + (group.rank if group else 0))
+        if group is not None and group.world > 1:
+            calls = {"sum": lambda: group.sum(a), "mean": lambda: group.mean(a, n * group.world), "max": lambda: group.max(a),
+                     "argmax": lambda: group.argmax(a, group.rank * n)}
+            call = calls[name]
+
+            def sharded():
+                call()
+                group.flush()  # the deferred combine belongs to this op's time
+
+            return sharded, 4 * n
         return getattr(a, name), 4 * n
     if name in ("sum_rows", "max_rows"):
         a = uni([n // 2048, 2048], 31)
@@ -100,10 +115,24 @@ def main():
     ap.add_argument("--peak", type=float, default=6454.6, help="HBM GB/s the fraction is quoted against")
     args = ap.parse_args()
 
+    import os
+
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if world > 1:
+        args.device = int(os.environ.get("LOCAL_RANK", "0"))
     plugin = pytorches_b200.load_plugin()
     if plugin.device_count() <= args.device:
         raise SystemExit("no CUDA device: the B200 plugin has no fallback")
     dev = Device(plugin, args.device)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from pytorches_b200.shard import ShardGroup
+
+        torch.cuda.set_device(args.device)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", args.device))
+        group = ShardGroup(dev, rank, world)
     get_stream = plugin.lib.pytorches_b200_stream
     get_stream.restype, get_stream.argtypes = ctypes.c_void_p, [ctypes.c_uint32]
     torch.cuda.set_device(args.device)
@@ -113,14 +142,23 @@ def main():
     if args.sweep:
         cases = [(name, (1 << 18) * 4 ** k) for name in OPS for k in range(7)]
     for name, n in cases:
-        fn, nbytes = build_case(name, n, dev)
+        fn, nbytes = build_case(name, n, dev, group)
+        if world > 1:
+            dist.barrier()
         ms = time_case(fn, stream, dev, args.iters, args.warmup)
+        if world > 1:  # the slowest rank's time, the bytes of all ranks
+            t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{args.device}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, nbytes = float(t.item()), nbytes * world
         gbs = nbytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"op": name, "elements": n, "bytes": nbytes, "ms": round(ms, 5), "GB/s": round(gbs, 1),
-                          "frac_of_peak": round(gbs / args.peak, 4), "frac_of_8TBps": round(gbs / 8000.0, 4),
-                          "larger_than_l2": nbytes > 126e6}))
-        sys.stdout.flush()
+        if rank == 0:
+            print(json.dumps({"op": name, "gpus": world, "elements": n * world, "bytes": nbytes, "ms": round(ms, 5), "GB/s": round(gbs, 1),
+                              "frac_of_peak": round(gbs / (args.peak * world), 4), "frac_of_8TBps": round(gbs / (8000.0 * world), 4),
+                              "larger_than_l2": nbytes > 126e6 * world}))
+            sys.stdout.flush()
         del fn
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
