@@ -443,6 +443,88 @@ __device__ __forceinline__ void scan_step(float v, uint64_t i, float &bv, uint64
 constexpr int MAX_CTA = 256;
 constexpr int MAX_UNROLL = 4;
 
+// The max/argmax counterpart of the sum's in-launch combine: CTA 0 gathers the segment maxima that the
+// worker CTAs publish through the mailbox ((epoch << 32) | float bits, stored with release semantics
+// AFTER the segment's position has been written to `seg_pos`), keeps the best (value, segment) pair -
+// NaN wins, then the larger value, then the lower segment - and writes the row's result. Max is
+// order-free, so all 256 threads poll and scan in parallel; polls are bounded.
+__device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v,
+                             int64_t *out_i, int64_t idx_offset, int *status) {
+    __shared__ float sv[8];
+    __shared__ uint64_t ss[8];
+    constexpr int WORDS = 8;
+    float bv = __int_as_float(0xff800000);
+    uint64_t bs = ~0ull;
+    bool failed = false;
+    for (uint64_t base = 0; base < segs; base += (uint64_t)MAX_CTA * WORDS) {
+        float v[WORDS];
+        uint32_t missing = 0;
+#pragma unroll
+        for (int k = 0; k < WORDS; ++k)
+            if (base + (uint64_t)k * MAX_CTA + threadIdx.x < segs) missing |= 1u << k;
+        const uint32_t mine = missing;
+        for (uint32_t tries = 0; tries < POLL_LIMIT && missing; ++tries) {
+#pragma unroll
+            for (int k = 0; k < WORDS; ++k)
+                if (missing & (1u << k)) {
+                    unsigned long long w;
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(mailbox + base + (uint64_t)k * MAX_CTA + threadIdx.x) : "memory");
+                    if ((uint32_t)(w >> 32) == epoch) {
+                        v[k] = __uint_as_float((uint32_t)w);
+                        missing &= ~(1u << k);
+                    }
+                }
+        }
+        failed = failed || missing != 0;
+#pragma unroll
+        for (int k = 0; k < WORDS; ++k)
+            if ((mine & ~missing) & (1u << k)) {
+                const uint64_t seg = base + (uint64_t)k * MAX_CTA + threadIdx.x;
+                if (bs == ~0ull) bs = seg;  // first segment this thread sees: position even if its value is -inf
+                scan_step(v[k], seg, bv, bs);
+            }
+    }
+    if (__syncthreads_or(failed)) {
+        if (threadIdx.x == 0) {
+            *(volatile int *)status = STATUS_WAIT_EXPIRED;
+            __threadfence_system();
+        }
+        return;
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const uint64_t os = __shfl_xor_sync(0xffffffffu, bs, d);
+        if (vi_better(ov, os, bv, bs)) { bv = ov; bs = os; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; ss[threadIdx.x >> 5] = bs; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        bv = threadIdx.x < 8 ? sv[threadIdx.x] : __int_as_float(0xff800000);
+        bs = threadIdx.x < 8 ? ss[threadIdx.x] : ~0ull;
+#pragma unroll
+        for (int d = 4; d >= 1; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+            const uint64_t os = __shfl_xor_sync(0xffffffffu, bs, d);
+            if (vi_better(ov, os, bv, bs)) { bv = ov; bs = os; }
+        }
+        if (threadIdx.x == 0) {
+            if (out_i) out_i[0] = seg_pos[bs] + idx_offset;
+            if (out_v) out_v[0] = bv;
+        }
+    }
+}
+
+// What a fused launch adds to max_rows_kernel's arguments (mailbox == nullptr: the plain two-pass form).
+struct MaxFused {
+    unsigned long long *mailbox;
+    uint32_t epoch;
+    float *final_v;
+    int64_t *final_i;
+    int64_t final_offset;
+    int *status;
+};
+
 // inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
 // threads share one task (32: a warp per task, 256: the CTA). VEC 4 requires every task start to be
 // 16-byte aligned (the host guarantees it). Writes the value and/or (ARG) the index within the row
@@ -450,9 +532,12 @@ constexpr int MAX_UNROLL = 4;
 template <int TPT, int VEC, bool ARG>
 __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
                                                            uint64_t segs, uint64_t seg_len, float *__restrict__ out_v,
-                                                           int64_t *__restrict__ out_i, int64_t idx_offset) {
+                                                           int64_t *__restrict__ out_i, int64_t idx_offset, const MaxFused fused) {
     constexpr int PER_CTA = MAX_CTA / TPT;
-    const uint64_t t = (uint64_t)blockIdx.x * PER_CTA + threadIdx.x / TPT;
+    if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
+        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status);
+    const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
+    const uint64_t t = cta * PER_CTA + threadIdx.x / TPT;
     const int lane = threadIdx.x % TPT;
     const bool live = t < tasks;
     // Every thread starts from (-inf, first index it will look at), so a slice of nothing but -inf
@@ -521,8 +606,14 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
         }
     }
     if (live && lane == 0) {
-        if (out_v) out_v[t] = bv;
-        if (ARG && out_i) out_i[t] = (int64_t)bi + idx_offset;
+        if (TPT == MAX_CTA && fused.mailbox != nullptr) {
+            if (ARG && out_i) out_i[t] = (int64_t)bi;  // position within the row, read by the combiner after the acquire
+            const unsigned long long w = ((unsigned long long)fused.epoch << 32) | __float_as_uint(bv);
+            asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(fused.mailbox + t), "l"(w) : "memory");
+        } else {
+            if (out_v) out_v[t] = bv;
+            if (ARG && out_i) out_i[t] = (int64_t)bi + idx_offset;
+        }
     }
 }
 
@@ -810,18 +901,29 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
         pi = arg ? (int64_t *)((char *)scratch + ((tasks * 4 + 15) & ~15ull)) : nullptr;
         off1 = 0;
     }
-    const unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
-#define B200_MAX_CASE(TPT, VEC)                                                                                                       \
-    if (m.tpt == TPT && m.vec == VEC) {                                                                                               \
-        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1);  \
-        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1);     \
+    unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
+    // A single long row: pick the best segment inside the same launch (see max_combiner).
+    MaxFused fused{};
+    if (outer == 1 && m.tpt == MAX_CTA && m.segs >= 64 && m.segs <= MAILBOX_SLOTS) {
+        int *status = reduce_status_word();
+        uint32_t epoch = 0;
+        unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
+        if (mailbox) {
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status};
+            grid += 1;
+        }
+    }
+#define B200_MAX_CASE(TPT, VEC)                                                                                                              \
+    if (m.tpt == TPT && m.vec == VEC) {                                                                                                      \
+        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);  \
+        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);     \
     }
     B200_MAX_CASE(32, 1)
     B200_MAX_CASE(32, 4)
     B200_MAX_CASE(256, 1)
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
-    if (m.segs > 1) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
+    if (m.segs > 1 && !fused.mailbox) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
     return cudaGetLastError();
 }
 
