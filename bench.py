@@ -39,9 +39,9 @@ OPS = ("sum", "mean", "max", "argmax")
 ORACLE_SO = os.path.join(ROOT, "oracle", "_build", "pytorches_plugin_cpuref.so")
 METRIC = "f32 elementwise/reduce HBM GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of sum_rows_tma_kernel from the ncu capture summarised in
-# profiles/sum_rows_tma_kernel_256mib.md (2^26 elements: 268.455 MB read, 4.1 MB written back from L2),
+# profiles/sum_rows_tma_kernel_256mib.md (2^26 elements: 268.495 MB read, 5.07 MB written back from L2),
 # read part scaled by 4 to this workload's 2^28 elements, write part kept.
-NCU_TRAFFIC_PER_LAUNCH = int(268.455e6 * 4 + 4.1e6)
+NCU_TRAFFIC_PER_LAUNCH = int(268.495e6 * 4 + 5.07e6)
 
 
 def uniform_pm1(n: int, seed: int, out: np.ndarray | None = None, first: int = 0) -> np.ndarray:
@@ -322,7 +322,7 @@ def main():
     if op_ev:
         sum_ms = statistics.mean(a.elapsed_time(b) for a, b in op_ev)
         achieved = 4 * N_ELEMS / (sum_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "sum_rows_tma_kernel (+ sum_combine_kernel): one SUM_AXIS over 2^28 f32", "achieved": round(achieved, 1),
+        roofline = {"bound": "hbm", "kernel": "sum_rows_tma_kernel<fused>: one SUM_AXIS over 2^28 f32 (streaming pass with the ordered combine in the same launch)", "achieved": round(achieved, 1),
                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_8TBps": round(achieved / 8000.0, 4),
                     "algorithmic_bytes_per_launch": 4 * N_ELEMS, "ms_per_launch": round(sum_ms, 5), "traffic": NCU_TRAFFIC_PER_LAUNCH}
     cpu = None
