@@ -16,9 +16,9 @@ namespace b200 {
 __device__ __forceinline__ float exp_ref(float x) {
     const bool is_nan = x != x;
     const bool too_big = x > 88.72284f;
-    // min/max as the SSE/AVX instructions define them: a NaN operand yields the second operand.
-    float xc = x < 88.72284f ? x : 88.72284f;
-    xc = xc > -103.97208f ? xc : -103.97208f;
+    // min(x, c) as SSE/AVX define it yields c for a NaN x; so does fminf, which is one instruction.
+    // (What a NaN lane computes is discarded anyway; xc itself is never NaN for the max.)
+    const float xc = fmaxf(fminf(x, 88.72284f), -103.97208f);
     const float n = rintf(__fmul_rn(xc, 1.44269504088896340736f));
     float r = __fmaf_rn(-n, 0.6933594f, xc);
     r = __fmaf_rn(-n, -2.1219444e-4f, r);
@@ -87,8 +87,7 @@ __device__ __forceinline__ float log_ref(float x) {
 __device__ __forceinline__ float tanh_ref(float x) {
     const bool is_nan = x != x;
     const float lim = 7.905311f;
-    float xc = x < lim ? x : lim;
-    xc = xc > -lim ? xc : -lim;
+    const float xc = fmaxf(fminf(x, lim), -lim);  // NaN x -> lim, like the AVX min; the lane is replaced below
     const float x2 = __fmul_rn(xc, xc);
     float p = -2.7607685e-16f;
     p = __fmaf_rn(p, x2, 2.0001879e-13f);
