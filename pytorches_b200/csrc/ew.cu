@@ -203,12 +203,12 @@ template <typename I> struct Pack<I, 4> {
     float4 v;
     __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) {
         if (istride) v = ld4(base + (uint64_t)c * 4);
-        else { const float s = *base; v = make_float4(s, s, s, s); }
+        else { const float s = __ldg(base); v = make_float4(s, s, s, s); }
     }
 };
 template <typename I> struct Pack<I, 1> {
     float v;
-    __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) { v = istride ? ld1(base + c) : *base; }
+    __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) { v = istride ? ld1(base + c) : __ldg(base); }
 };
 
 template <class Fn, typename I, int VEC>
