@@ -274,7 +274,11 @@ def main():
     l1 = launches()
     ms = ev[0].elapsed_time(ev[1])
     t_ms = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+    rank_ms = [ms]
     if world > 1:
+        all_ms = [torch.zeros_like(t_ms) for _ in range(world)]
+        dist.all_gather(all_ms, t_ms)
+        rank_ms = [float(t.item()) for t in all_ms]
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms = float(t_ms.item())
     bytes_per_step = len(OPS) * 4 * N_ELEMS * world
@@ -338,7 +342,7 @@ def main():
                    "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s), partials all-gathered over NCCL and combined by plugin ops" if world > 1 else "none",
                    "l2": "input (1 GiB) is larger than L2 (126 MB); no flush needed", "frac_of_measured_peak": round(value / (peak * world), 4),
                    "frac_of_8TBps": round(value / (8000.0 * world), 4)},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "roofline": roofline, "cpu_baseline": cpu,
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "rank_ms_per_step": [round(v / args.steps, 4) for v in rank_ms], "roofline": roofline, "cpu_baseline": cpu,
         "ops_ms": {k: round(v, 5) for k, v in per_op.items()}, "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
     }
     sys.stdout.flush()

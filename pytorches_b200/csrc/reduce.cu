@@ -16,6 +16,7 @@
 //
 // All kernels are pure HBM streaming: every load of a thread's batch is issued before the first use.
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up at run time, libcuda is not linked
@@ -749,7 +750,14 @@ namespace {
 // kept for the life of the process. Each launch gets the next epoch (never 0); when the 32-bit epoch
 // wraps the words are zeroed again, on the stream, so no stale word can match.
 constexpr uint64_t MAILBOX_SLOTS = 1ull << 20;  // one per 65536 elements: rows of up to 2^36 elements
+// PYTORCHES_B200_FUSED_COMBINE=0 in the environment turns the in-launch combines off (two launches
+// per reduction instead of one); a diagnostic switch, read once.
 unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
+    static const bool enabled = [] {
+        const char *e = getenv("PYTORCHES_B200_FUSED_COMBINE");
+        return !(e && e[0] == '0');
+    }();
+    if (!enabled) return nullptr;
     static std::mutex mu;
     static unsigned long long *box[64] = {};
     static uint32_t next[64] = {};
