@@ -284,6 +284,23 @@ def main():
     bytes_per_step = len(OPS) * 4 * N_ELEMS * world
     value = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
 
+    # ---- N > 1: the same four passes on every rank with NO exchange, all ranks at once. The gap between
+    # the sharded step and the slowest rank's local passes is what the exchange and the combines cost. ----
+    local_ms = None
+    if world > 1:
+        k_local = min(args.steps, 20)
+        barrier()
+        la, lb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        la.record(stream)
+        for _ in range(k_local):
+            r = [x.sum(), x.mean(), x.max(), x.argmax()]
+        lb.record(stream)
+        barrier()
+        mine = torch.tensor([la.elapsed_time(lb) / k_local], dtype=torch.float64, device=f"cuda:{local}")
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        local_ms = [round(float(t.item()), 4) for t in every]
+
     # ---- per-op device times (N = 1): every op alone, K launches each, for the breakdown ----
     per_op = {}
     if world == 1:
@@ -342,7 +359,8 @@ def main():
                    "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s), partials all-gathered over NCCL and combined by plugin ops" if world > 1 else "none",
                    "l2": "input (1 GiB) is larger than L2 (126 MB); no flush needed", "frac_of_measured_peak": round(value / (peak * world), 4),
                    "frac_of_8TBps": round(value / (8000.0 * world), 4)},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "rank_ms_per_step": [round(v / args.steps, 4) for v in rank_ms], "roofline": roofline, "cpu_baseline": cpu,
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "rank_ms_per_step": [round(v / args.steps, 4) for v in rank_ms],
+        "rank_local_ms_per_step_no_exchange": local_ms, "roofline": roofline, "cpu_baseline": cpu,
         "ops_ms": {k: round(v, 5) for k, v in per_op.items()}, "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
     }
     sys.stdout.flush()

@@ -372,6 +372,86 @@ def check_max_argmax_against_torch(p):
     assert exec_op(p, op.ARGMAX_AXIS, [0], [(x, (12,), (1,))], out, ()) == abi.STATUS_UNSUPPORTED
 
 
+def check_concurrent_threads(p):
+    """docs/plugin-abi.md:228-236: every entry point may be called from any number of threads; calls into
+    one device behave as if serialized; last_error is per thread. Eight threads each run their own chain
+    of allocations, ops, reductions and frees on device 0 at once; every result must be what the chain
+    yields alone (the ops used are bit-exact), and a thread that provokes errors is the only one to see them."""
+    import threading
+
+    n_threads, rounds = 8, 12
+    failures: list = []
+    sums: dict = {}
+
+    def size(tid, k):  # odd sizes, different per thread: different buckets and kernels; the last two
+        return (1000 + 4099 * tid if tid < 6 else 66000 + 1111 * tid) + 37 * k  # reach the long-row reductions
+
+    def sum_of(buf, n):
+        r = Buf.empty(p, 1)
+        assert exec_op(p, op.SUM_AXIS, [0], [(buf, (n,), (1,))], r, ()) == abi.STATUS_OK
+        v = r.get()[0]
+        r.free()
+        return v
+    start = threading.Barrier(n_threads)
+
+    def expected(a, b, k):
+        y = (a + b) * np.float32(k + 1)
+        y = np.maximum(y, np.float32(0)) - a
+        return y
+
+    def worker(tid: int):
+        try:
+            start.wait()
+            for k in range(rounds):
+                n = size(tid, k)
+                a_h, b_h = lcg_data(n, 100 + tid), lcg_data(n, 200 + tid + k)
+                a, b = Buf(p, a_h), Buf(p, b_h)
+                s = Buf(p, np.full(1, k + 1, dtype=np.float32))
+                t0, t1, t2, out = (Buf.empty(p, n) for _ in range(4))
+                sh, st = (n,), (1,)
+                assert exec_op(p, op.ADD, [0], [(a, sh, st), (b, sh, st)], t0, sh) == abi.STATUS_OK
+                assert exec_op(p, op.MUL, [0], [(t0, sh, st), (s, sh, (0,))], t1, sh) == abi.STATUS_OK
+                assert exec_op(p, op.RELU, [0], [(t1, sh, st)], t2, sh) == abi.STATUS_OK
+                assert exec_op(p, op.SUB, [0], [(t2, sh, st), (a, sh, st)], out, sh) == abi.STATUS_OK
+                want = expected(a_h, b_h, k)
+                assert_bit_equal(f"thread {tid} round {k}", out.get(), want)
+                # a reduction too: it takes scratch from the allocator the other threads are using
+                m = Buf.empty(p, 1)
+                assert exec_op(p, op.MAX_AXIS, [0], [(out, sh, st)], m, ()) == abi.STATUS_OK
+                assert m.get()[0] == want.max()
+                sums[(tid, k)] = sum_of(out, n)
+                if tid == 0:
+                    # errors stay with the thread that made them
+                    assert exec_op(p, 9999, [0], [(a, sh, st)], out, sh) == abi.STATUS_UNSUPPORTED
+                    assert p.last_error()
+                for buf in (a, b, s, t0, t1, t2, out, m):
+                    buf.free()
+        except BaseException as e:  # noqa: BLE001 - reported to the main thread
+            failures.append((tid, repr(e)))
+            try:
+                start.abort()
+            except Exception:
+                pass
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(n_threads)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures
+    # the ordered sums computed under contention carry the bits the same call yields alone
+    for (tid, k), got in sorted(sums.items()):
+        want = Buf(p, expected(lcg_data(size(tid, k), 100 + tid), lcg_data(size(tid, k), 200 + tid + k), k))
+        alone = sum_of(want, size(tid, k))
+        assert f32_bits(got) == f32_bits(alone), (tid, k, got, alone)
+        want.free()
+    # the main thread made no failing call since its last successful one: the others' errors are not its own
+    x = Buf(p, lcg_data(8, 3))
+    out = Buf.empty(p, 8)
+    assert exec_op(p, op.NEG, [0], [(x, (8,), (1,))], out, (8,)) == abi.STATUS_OK
+    assert_bit_equal("neg after threads", out.get(), -lcg_data(8, 3))
+
+
 ALL_CHECKS = [
     check_binary_broadcast_patterns,
     check_sum_axis_layouts,
@@ -386,4 +466,5 @@ ALL_CHECKS = [
     check_zero_sized_and_scalars,
     check_diff_against_torch,
     check_max_argmax_against_torch,
+    check_concurrent_threads,
 ]
