@@ -199,7 +199,7 @@ def main():
 
     import pytorches_b200
     from pytorches_b200.core import Device, Tensor
-    from pytorches_b200.shard import ShardGroup
+    from pytorches_b200.shard import ShardGroup, nccl_options
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -211,7 +211,7 @@ def main():
         raise SystemExit(f"the B200 plugin sees {plugin.device_count()} device(s); rank needs device {local} (there is no CPU fallback)")
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=nccl_options())
     dev = Device(plugin, local)
     group = ShardGroup(dev, rank, world)
     get_stream = plugin.lib.pytorches_b200_stream

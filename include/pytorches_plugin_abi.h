@@ -94,7 +94,21 @@ enum {
     PT_OP_FILL = 400,        /* no inputs; ints[0] = f32 bit pattern */
     PT_OP_RAND_NORMAL = 401, /* no inputs; ints[0] = seed; counter-based Box-Muller, see below */
 
-    PT_OP_AXPY = 500 /* optional; out = in0 + alpha*in1, alpha bits in ints[0]; out may alias in0 */
+    PT_OP_AXPY = 500, /* optional; out = in0 + alpha*in1, alpha bits in ints[0]; out may alias in0 */
+
+    /* Appended by this plugin, NOT in the reference: optional fused ops, each with a fallback in the
+     * host (the core asks supports_op and otherwise issues the two ops it stands for), as AXPY has.
+     * The reference names them as its next ABI candidates ("a relu gradient, bias plus activation",
+     * docs/plugin-abi.md:285-287; TODO.md:270). Operands follow the binary-op contract: both inputs
+     * are described with the output's shape and their own strides (0 = broadcast). Each is DEFINED
+     * as its two-op sequence through a contiguous intermediate, bit for bit:
+     *   RELU_GRAD: out = MUL(in0, STEP(in1))   the gradient the core builds for relu
+     *                                          (crates/core/src/lib.rs:639-643); in0 = g, in1 = x
+     *   ADD_RELU:  out = RELU(ADD(in0, in1))   bias plus activation
+     *   SUB_EXP:   out = EXP(SUB(in0, in1))    the numerator of a row softmax: exp(x - rowmax) */
+    PT_OP_RELU_GRAD = 501,
+    PT_OP_ADD_RELU = 502,
+    PT_OP_SUB_EXP = 503
 };
 
 /*

@@ -131,6 +131,7 @@ uint32_t supports_op(uint32_t code) {
         case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV:
         case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY: case OP_SUM_AXIS: case OP_COPY: case OP_FILL: case OP_RAND_NORMAL:
         case OP_MAX_AXIS: case OP_ARGMAX_AXIS: case OP_MAX_ARGMAX_AXIS: case OP_ARGMAX_COMBINE:
+        case OP_RELU_GRAD: case OP_ADD_RELU: case OP_SUB_EXP:
             return 1;
         default: return 0;
     }
@@ -182,7 +183,8 @@ PtStatus run(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint3
         case OP_FILL: case OP_RAND_NORMAL: need = 0; break;
         case OP_NEG: case OP_EXP: case OP_LOG: case OP_RELU: case OP_TANH: case OP_STEP: case OP_COPY:
         case OP_SUM_AXIS: case OP_MAX_AXIS: case OP_ARGMAX_AXIS: need = 1; break;
-        case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV: case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY: need = 2; break;
+        case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV: case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY:
+        case OP_RELU_GRAD: case OP_ADD_RELU: case OP_SUB_EXP: need = 2; break;
         default: return PT_STATUS_UNSUPPORTED;
     }
     if (n_in != need) return PT_STATUS_INVALID_ARGUMENT;
@@ -206,6 +208,24 @@ PtStatus run(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint3
             if (!same_shape(ins[0], o) || !same_shape(ins[1], o)) return PT_STATUS_INVALID_ARGUMENT;
             binary(op, (const float *)ins[0].data, ins[0].strides, (const float *)ins[1].data, ins[1].strides, o.shape, o.ndim, out);
             break;
+        case OP_RELU_GRAD: case OP_ADD_RELU: case OP_SUB_EXP: {
+            // The appended fused ops are DEFINED as the two reference ops they stand for, run one after
+            // the other through a contiguous intermediate; here they are computed exactly that way.
+            if (!same_shape(ins[0], o) || !same_shape(ins[1], o)) return PT_STATUS_INVALID_ARGUMENT;
+            if (n == 0) break;
+            std::vector<float> mid(n);
+            std::vector<uint64_t> dense(o.ndim ? o.ndim : 1, 1);
+            for (size_t d = o.ndim; d-- > 1;) dense[d - 1] = dense[d] * o.shape[d];
+            const float *a = (const float *)ins[0].data, *b = (const float *)ins[1].data;
+            if (op == OP_RELU_GRAD) {  // MUL(g, STEP(x)), crates/core/src/lib.rs:639-643
+                unary(OP_STEP, b, o.shape, ins[1].strides, o.ndim, mid.data());
+                binary(OP_MUL, a, ins[0].strides, mid.data(), dense.data(), o.shape, o.ndim, out);
+            } else {
+                binary(op == OP_ADD_RELU ? OP_ADD : OP_SUB, a, ins[0].strides, b, ins[1].strides, o.shape, o.ndim, mid.data());
+                unary(op == OP_ADD_RELU ? OP_RELU : OP_EXP, mid.data(), o.shape, dense.data(), o.ndim, out);
+            }
+            break;
+        }
         case OP_AXPY: {
             if (numel(ins[0].shape, ins[0].ndim) != n || numel(ins[1].shape, ins[1].ndim) != n) return PT_STATUS_INVALID_ARGUMENT;
             uint32_t bits = (uint32_t)attrs.ints[0];

@@ -26,6 +26,7 @@ enum : uint32_t {
     OP_MATMUL = 200, OP_SUM_AXIS = 201, OP_MATMUL_T = 202, OP_MAX_AXIS = 203, OP_ARGMAX_AXIS = 204,
     OP_MAX_ARGMAX_AXIS = 205, OP_ARGMAX_COMBINE = 206,
     OP_COPY = 300, OP_FILL = 400, OP_RAND_NORMAL = 401, OP_AXPY = 500,
+    OP_RELU_GRAD = 501, OP_ADD_RELU = 502, OP_SUB_EXP = 503,  // appended fused ops (not in the reference)
 };
 
 constexpr size_t CHUNK = size_t(1) << 16;    // ew.rs:13

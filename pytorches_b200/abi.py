@@ -27,7 +27,7 @@ MEMORY_UNKNOWN = 2**64 - 1
 
 
 class op:
-    """Op codes (crates/plugin-abi/src/lib.rs:67-115); 203-206 are appended codes."""
+    """Op codes (crates/plugin-abi/src/lib.rs:67-115); 203-206 and 501-503 are appended codes."""
 
     NEG, EXP, LOG, RELU, TANH, STEP = 1, 2, 3, 4, 5, 6
     ADD, SUB, MUL, DIV = 100, 101, 102, 103
@@ -37,6 +37,7 @@ class op:
     COPY = 300
     FILL, RAND_NORMAL = 400, 401
     AXPY = 500
+    RELU_GRAD, ADD_RELU, SUB_EXP = 501, 502, 503  # appended: optional fused ops, each equal to its two-op sequence
 
 
 class TensorDesc(C.Structure):

@@ -72,7 +72,7 @@ def config1(dev: Device):
     def step():
         for t in (A, b, s):
             t.grad = None
-        out = (A + b).relu() * s
+        out = A.add_relu(b) * s  # ADD then RELU (and STEP then MUL in backward) unless the device uses the fused ops
         r = out.sum_dim(1)
         out.sum().backward()
         return r, A.grad, b.grad, s.grad
@@ -98,7 +98,7 @@ def config3(dev: Device, layers: int = 12, width: int = 8192, batch: int = 32):
         loss.backward()                                                # gradient of the mean back to `last`
         g = last.grad
         for a in acts:                                                 # ReLU backward: g * STEP(x)
-            g_in = g.raw_binary(a.raw_unary(op.STEP), op.MUL)
+            g_in = g.relu_grad(a)
         opt.step()                                                     # AXPY per parameter tensor
         return loss, g_in
 
@@ -119,16 +119,16 @@ def config4(dev: Device, transposed: bool, B: int = 64, R: int = 2048, Cn: int =
             Y1 = X + m1
         Y = Y1 + m2
         M = Y.max_dim(2, keepdim=True)
-        E = (Y - M).exp()
+        E = Y.sub_exp(M)  # SUB then EXP unless the device uses the fused op
         S = E.sum_dim(2, keepdim=True)
         return E / S
 
     return step
 
 
-def measure(name: str, make, plugin: Plugin, device_index: int, iters: int, stream=None):
+def measure(name: str, make, plugin: Plugin, device_index: int, iters: int, stream=None, fused: bool = False):
     counting = CountingPlugin(plugin)
-    dev = Device(counting, device_index)
+    dev = Device(counting, device_index, fused=fused)
     step = make(dev)
     step()  # warm-up, also fills the allocator's cache
     dev.synchronize()
@@ -166,6 +166,9 @@ def main():
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--cpu", action="store_true", help="also time the CPU oracle (test infrastructure) on the same configs")
     ap.add_argument("--peak", type=float, default=6454.6)
+    ap.add_argument("--fused", action="store_true",
+                    help="also run each config with the optional fused ops (RELU_GRAD, ADD_RELU, SUB_EXP) in place of the reference's "
+                         "two-op sequences; same results, fewer bytes")
     args = ap.parse_args()
     makers = {"1": ("config 1: bias+relu+scale, row sums, backward", config1),
               "3": ("config 3: MLP elementwise part + SGD over 805M parameters", config3),
@@ -194,6 +197,12 @@ def main():
             r["cpu_oracle_ms"], r["cpu_oracle_GB/s"], r["cpu_threads"] = c["ms"], c["GB/s"], os.cpu_count()
         print(json.dumps(r))
         sys.stdout.flush()
+        if args.fused:
+            f = measure(title + " [fused ops]", make, plugin, args.device, args.iters, stream, fused=True)
+            f["speedup_vs_reference_sequence"] = round(r["ms"] / f["ms"], 3)
+            f["GB/s_of_reference_sequence_bytes"] = round(r["algorithmic_bytes"] / (f["ms"] * 1e-3) / 1e9, 1)
+            print(json.dumps(f))
+            sys.stdout.flush()
 
 
 if __name__ == "__main__":

@@ -9,7 +9,10 @@ plugin the way the real core would. Method names and argument meaning follow the
 cites the function it mirrors. It holds no kernels and no numeric code of its own.
 
 Not in the reference (appended ops 203/204): ``sum_dim``, ``max_dim``, ``argmax_dim``, ``max``,
-``argmax``.
+``argmax``. Also not in the reference: the optional fused ops 501-503 (``add_relu``, ``sub_exp`` and
+the one-op relu gradient). They are used only on a device created with ``fused=True`` whose plugin
+offers them (``supports_op``, as for ``axpy_``); otherwise, and by default, the two-op sequence of the
+reference core runs. Either way the results carry the same bits.
 """
 
 from __future__ import annotations
@@ -31,10 +34,10 @@ def _f32_bits(v: float) -> int:
 class Device:
     """One device of one plugin (crates/core/src/lib.rs:141-186)."""
 
-    def __init__(self, plugin: Plugin, index: int = 0):
+    def __init__(self, plugin: Plugin, index: int = 0, fused: bool = False):
         if index >= plugin.device_count():
             raise ValueError(f"{plugin.name}:{index} does not exist ({plugin.device_count()} devices)")
-        self.plugin, self.index = plugin, index
+        self.plugin, self.index, self.fused = plugin, index, fused
 
     def __eq__(self, other):
         return isinstance(other, Device) and other.plugin is self.plugin and other.index == self.index
@@ -50,6 +53,10 @@ class Device:
 
     def supports_op(self, code: int) -> bool:
         return self.plugin.supports_op(code)
+
+    def offers_fused(self, code: int) -> bool:
+        """Whether an optional fused op (501-503) is to be used instead of its two-op sequence."""
+        return self.fused and self.plugin.supports_op(code)
 
 
 class Buffer:
@@ -283,7 +290,42 @@ class Tensor:
 
     def relu(self) -> "Tensor":
         x = self.detach()
-        return self.raw_unary(op.RELU).attach([self], lambda g: [g.mul(x.raw_unary(op.STEP))])
+        return self.raw_unary(op.RELU).attach([self], lambda g: [g.relu_grad(x)])
+
+    def relu_grad(self, x: "Tensor") -> "Tensor":
+        """``self * step(x)``, the gradient of relu (lib.rs:639-643): RELU_GRAD when offered, else STEP then MUL."""
+        if self.device.offers_fused(op.RELU_GRAD):
+            return self.raw_binary(x, op.RELU_GRAD)
+        return self.mul(x.raw_unary(op.STEP))
+
+    # ---- fused forward ops (appended, optional): same values and gradients as the two ops they replace ----
+    def add_relu(self, o: "Tensor") -> "Tensor":
+        """``(self + o).relu()``: bias plus activation in one pass when the plugin offers ADD_RELU."""
+        if not self.device.offers_fused(op.ADD_RELU):
+            return self.add(o).relu()
+        sa, sb = list(self.shape), list(o.shape)
+        out = self.raw_binary(o, op.ADD_RELU)
+        y = out.detach()  # step(relu(t)) == step(t): the output stands in for the pre-activation
+
+        def back(g):
+            gt = g.relu_grad(y)
+            return [gt.unbroadcast(sa), gt.unbroadcast(sb)]
+
+        return out.attach([self, o], back)
+
+    def sub_exp(self, o: "Tensor") -> "Tensor":
+        """``(self - o).exp()``, the numerator of a softmax, in one pass when the plugin offers SUB_EXP."""
+        if not self.device.offers_fused(op.SUB_EXP):
+            return self.sub(o).exp()
+        sa, sb = list(self.shape), list(o.shape)
+        out = self.raw_binary(o, op.SUB_EXP)
+        y = out.detach()
+
+        def back(g):
+            gt = g.mul(y)
+            return [gt.unbroadcast(sa), gt.neg().unbroadcast(sb)]
+
+        return out.attach([self, o], back)
 
     def tanh(self) -> "Tensor":
         out = self.raw_unary(op.TANH)

@@ -27,6 +27,7 @@ namespace {
 enum : uint32_t {
     OP_NEG = 1, OP_EXP = 2, OP_LOG = 3, OP_RELU = 4, OP_TANH = 5, OP_STEP = 6,
     OP_ADD = 100, OP_SUB = 101, OP_MUL = 102, OP_DIV = 103, OP_COPY = 300,
+    OP_RELU_GRAD = 501, OP_ADD_RELU = 502, OP_SUB_EXP = 503,
 };
 
 // ---- per-element functors ------------------------------------------------------------------------
@@ -88,11 +89,33 @@ template <class Fn> __device__ __forceinline__ float apply_unary(float v, bool l
     return Fn::f(v);
 }
 
+// TAIL: the op ends in EXP, whose last (n mod 8) output elements the reference computes with libm.
 template <uint32_t OP> struct BinaryFn;
-template <> struct BinaryFn<OP_ADD> { __device__ __forceinline__ static float f(float a, float b) { return __fadd_rn(a, b); } };
-template <> struct BinaryFn<OP_SUB> { __device__ __forceinline__ static float f(float a, float b) { return __fsub_rn(a, b); } };
-template <> struct BinaryFn<OP_MUL> { __device__ __forceinline__ static float f(float a, float b) { return __fmul_rn(a, b); } };
-template <> struct BinaryFn<OP_DIV> { __device__ __forceinline__ static float f(float a, float b) { return __fdiv_rn(a, b); } };
+template <> struct BinaryFn<OP_ADD> { static constexpr bool TAIL = false; __device__ __forceinline__ static float f(float a, float b) { return __fadd_rn(a, b); } };
+template <> struct BinaryFn<OP_SUB> { static constexpr bool TAIL = false; __device__ __forceinline__ static float f(float a, float b) { return __fsub_rn(a, b); } };
+template <> struct BinaryFn<OP_MUL> { static constexpr bool TAIL = false; __device__ __forceinline__ static float f(float a, float b) { return __fmul_rn(a, b); } };
+template <> struct BinaryFn<OP_DIV> { static constexpr bool TAIL = false; __device__ __forceinline__ static float f(float a, float b) { return __fdiv_rn(a, b); } };
+// The appended fused ops: each is the two reference ops it names, applied one after the other to the
+// element, so the result carries the bits of the two-op sequence (the intermediate of that sequence
+// is an f32 tensor; here it is an f32 register).
+//   RELU_GRAD = MUL(g, STEP(x)): a real multiply by 1 or 0, so that g = -3 gives -0 and g = inf gives NaN
+//   exactly as the sequence does.
+template <> struct BinaryFn<OP_RELU_GRAD> {
+    static constexpr bool TAIL = false;
+    __device__ __forceinline__ static float f(float g, float x) { return __fmul_rn(g, UnaryFn<OP_STEP>::f(x)); }
+};
+template <> struct BinaryFn<OP_ADD_RELU> {
+    static constexpr bool TAIL = false;
+    __device__ __forceinline__ static float f(float a, float b) { return UnaryFn<OP_RELU>::f(__fadd_rn(a, b)); }
+};
+// SUB_EXP = EXP(SUB(a, b)). The EXP of the sequence reads a contiguous intermediate, so the reference
+// computes all but the last (n mod 8) elements of the whole output with its polynomial and those few
+// with libm (plugins/cpu/src/ew.rs:114-138,160); `libm` is applied to them by a second, tiny launch.
+template <> struct BinaryFn<OP_SUB_EXP> {
+    static constexpr bool TAIL = true;
+    __device__ __forceinline__ static float f(float a, float b) { return exp_ref(__fsub_rn(a, b)); }
+    __device__ __noinline__ static float libm(float a, float b) { return UnaryFn<OP_EXP>::libm(__fsub_rn(a, b)); }
+};
 
 // ---- memory access helpers --------------------------------------------------------------------------
 // Inputs are read once: bypass L1 allocation. Outputs are written once: streaming stores.
@@ -482,6 +505,23 @@ __global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restric
     else out[i] = apply_unary<Fn>(a[off[0]], Fn::SPLIT && split.uses_libm(i));
 }
 
+// The last (n mod 8) elements of a binary op that ends in a libm-split function: one thread each.
+template <class Fn>
+__global__ void __launch_bounds__(32) binary_tail_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
+                                                         const __grid_constant__ GatherPlan<2> p, uint64_t first) {
+    const uint64_t i = first + threadIdx.x;
+    if (i >= p.n) return;
+    uint64_t rem = i, off[2] = {0, 0};
+    for (int d = 0; d < p.nd; ++d) {
+        uint64_t q, r;
+        p.size[d].divmod(rem, q, r);
+        rem = q;
+        off[0] += r * p.stride[0][d];
+        off[1] += r * p.stride[1][d];
+    }
+    if constexpr (Fn::TAIL) out[i] = Fn::libm(a[off[0]], b[off[1]]);
+}
+
 // ---- AXPY, FILL, RAND_NORMAL --------------------------------------------------------------------------
 // out = a + alpha*b. The reference fuses the multiply-add (one rounding) for every element except
 // the last n mod 8, which it computes with two roundings (plugins/cpu/src/ew.rs:316-329; its chunks
@@ -731,7 +771,7 @@ template <int NOPS> GatherPlan<NOPS> make_gather_plan(const EwProblem &p) {
     return g;
 }
 
-template <class Fn> cudaError_t run_binary(const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s) {
+template <class Fn> cudaError_t run_binary_body(const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s) {
     // Flat: one dim (or none) and inner strides in {0,1}.
     if (p.nd <= 1) {
         const uint64_t sa = p.nd ? p.dim[0].stride[0] : 0, sb = p.nd ? p.dim[0].stride[1] : 0;
@@ -778,6 +818,18 @@ template <class Fn> cudaError_t run_binary(const float *a, const float *b, float
     auto g = make_gather_plan<2>(p);
     B200_LAUNCH((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g, LibmSplit{});
     return cudaGetLastError();
+}
+
+template <class Fn> cudaError_t run_binary(const float *a, const float *b, float *out, const EwProblem &p, cudaStream_t s) {
+    cudaError_t e = run_binary_body<Fn>(a, b, out, p, s);
+    if constexpr (Fn::TAIL) {
+        if (e == cudaSuccess && (p.n & 7)) {  // ordered behind the body on the same stream: overwrites its last few elements
+            auto g = make_gather_plan<2>(p);
+            B200_LAUNCH((binary_tail_kernel<Fn>), 1, 32, 0, s, a, b, out, g, p.n - (p.n & 7));
+            e = cudaGetLastError();
+        }
+    }
+    return e;
 }
 
 template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwProblem &p, cudaStream_t s) {
@@ -847,6 +899,9 @@ cudaError_t launch_binary(uint32_t op, const float *a, const float *b, float *ou
         case OP_SUB: return run_binary<BinaryFn<OP_SUB>>(a, b, out, p, s);
         case OP_MUL: return run_binary<BinaryFn<OP_MUL>>(a, b, out, p, s);
         case OP_DIV: return run_binary<BinaryFn<OP_DIV>>(a, b, out, p, s);
+        case OP_RELU_GRAD: return run_binary<BinaryFn<OP_RELU_GRAD>>(a, b, out, p, s);
+        case OP_ADD_RELU: return run_binary<BinaryFn<OP_ADD_RELU>>(a, b, out, p, s);
+        case OP_SUB_EXP: return run_binary<BinaryFn<OP_SUB_EXP>>(a, b, out, p, s);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -316,6 +316,7 @@ uint32_t supports_op(uint32_t code) {
         case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS:
         case PT_OP_MAX_ARGMAX_AXIS: case PT_OP_ARGMAX_COMBINE:
         case PT_OP_COPY: case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_AXPY:
+        case PT_OP_RELU_GRAD: case PT_OP_ADD_RELU: case PT_OP_SUB_EXP:
             return 1;
         default:
             return 0;
@@ -384,6 +385,7 @@ const char *op_name(uint32_t op) {
         case PT_OP_MAX_AXIS: return "MAX_AXIS"; case PT_OP_ARGMAX_AXIS: return "ARGMAX_AXIS"; case PT_OP_COPY: return "COPY";
         case PT_OP_MAX_ARGMAX_AXIS: return "MAX_ARGMAX_AXIS"; case PT_OP_ARGMAX_COMBINE: return "ARGMAX_COMBINE";
         case PT_OP_FILL: return "FILL"; case PT_OP_RAND_NORMAL: return "RAND_NORMAL"; case PT_OP_AXPY: return "AXPY";
+        case PT_OP_RELU_GRAD: return "RELU_GRAD"; case PT_OP_ADD_RELU: return "ADD_RELU"; case PT_OP_SUB_EXP: return "SUB_EXP";
         default: return "?";
     }
 }
@@ -452,7 +454,8 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
         case PT_OP_FILL: case PT_OP_RAND_NORMAL: need = 0; break;
         case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP: case PT_OP_COPY:
         case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS: need = 1; break;
-        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_AXPY: need = 2; break;
+        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_AXPY:
+        case PT_OP_RELU_GRAD: case PT_OP_ADD_RELU: case PT_OP_SUB_EXP: need = 2; break;
         default:
             set_err("b200: op %u is not implemented", op);
             return PT_STATUS_UNSUPPORTED;
@@ -494,7 +497,8 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
             e = launch_unary(op, (const float *)ins[0].data, out, p, d.stream);
             break;
         }
-        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: {
+        case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV:
+        case PT_OP_RELU_GRAD: case PT_OP_ADD_RELU: case PT_OP_SUB_EXP: {
             if (!same_shape(ins[0], o) || !same_shape(ins[1], o)) B200_INVALID("b200: %s: operand shapes differ from the output's", op_name(op));
             if (n == 0) break;
             EwProblem p;

@@ -128,10 +128,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        from pytorches_b200.shard import ShardGroup
+        from pytorches_b200.shard import ShardGroup, nccl_options
 
         torch.cuda.set_device(args.device)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", args.device))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", args.device), pg_options=nccl_options())
         group = ShardGroup(dev, rank, world)
     get_stream = plugin.lib.pytorches_b200_stream
     get_stream.restype, get_stream.argtypes = ctypes.c_void_p, [ctypes.c_uint32]

@@ -42,6 +42,30 @@ def split_layers(n_layers: int, rank: int, world: int) -> tuple[int, int]:
     return split_rows(n_layers, rank, world)
 
 
+def nccl_options():
+    """Process-group options for the exchanges of this path: partials of 4 to 12 bytes per rank.
+
+    Left alone, NCCL sizes its kernels for bandwidth: at 8 ranks an all-gather occupies many CTAs that
+    spin on their peers while the next local pass is streaming on the same GPU, and that pass loses
+    the SMs they hold. One CTA moves these few bytes just as fast. ``PYTORCHES_B200_NCCL_CTAS=0``
+    keeps the library's own choice (for comparison); any other number is the CTA limit.
+
+    The exchange is meant to run BESIDE the next local pass, but both become runnable at the same
+    moment and the pass has thousands of CTAs queued: at equal priority the collective's one CTA can
+    wait behind all of them, so it starts when the pass ends and its latency (which grows with the
+    number of ranks) is paid in full. The communication stream is therefore a high-priority stream:
+    its CTA takes the first slot that frees up. ``PYTORCHES_B200_NCCL_PRIORITY=0`` turns that off."""
+    import os
+
+    ctas = int(os.environ.get("PYTORCHES_B200_NCCL_CTAS", "1"))
+    high = os.environ.get("PYTORCHES_B200_NCCL_PRIORITY", "1") != "0"
+    opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=high)
+    if ctas > 0:
+        opts.config.min_ctas = 1
+        opts.config.max_ctas = ctas
+    return opts
+
+
 class _CudaView:
     """Exposes a device allocation of the plugin through ``__cuda_array_interface__`` (no copy)."""
 

@@ -372,6 +372,64 @@ def check_max_argmax_against_torch(p):
     assert exec_op(p, op.ARGMAX_AXIS, [0], [(x, (12,), (1,))], out, ()) == abi.STATUS_UNSUPPORTED
 
 
+FUSED = {  # fused code -> (first op, second op, which input the first op reads: None = both)
+    op.RELU_GRAD: (op.STEP, op.MUL),
+    op.ADD_RELU: (op.ADD, op.RELU),
+    op.SUB_EXP: (op.SUB, op.EXP),
+}
+
+
+def check_fused_ops_equal_their_sequences(p):
+    """The appended optional ops 501-503 are defined as two reference ops run one after the other
+    (docs/plugin-abi.md:285-287 names them as candidates; crates/core/src/lib.rs:639-643 is the relu
+    gradient). A plugin need not offer them; one that does must give the sequence's bits on every layout."""
+    offered = [c for c in FUSED if p.supports_op(c)]
+    cases = [
+        ((1000,), (1,), (1,)), ((4099,), (1,), (0,)), ((7,), (1,), (1,)), ((70_003,), (1,), (1,)),
+        ((37, 91), (91, 1), (0, 1)), ((64, 128), (128, 1), (1, 0)), ((8, 16, 32), (512, 32, 1), (0, 1, 0)),
+        ((33, 65), (1, 33), (65, 1)), ((8, 64, 128), (8192, 1, 64), (128, 0, 1)), ((2, 3, 4), (1, 2, 6), (12, 4, 1)), ((), (), ()),
+    ]
+    specials = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, -3.0, 3.0, 1e-45, 89.0, -104.0], dtype=np.float32)
+    for shape, sa, sb in cases:
+        n = int(np.prod(shape)) if shape else 1
+        span = lambda st: 1 + sum((d - 1) * t for d, t in zip(shape, st))
+        av, bv = lcg_data(span(sa), 41) * np.float32(12.0), lcg_data(span(sb), 42)
+        av[: min(av.size, specials.size)] = specials[: av.size]
+        bv[: min(bv.size, specials.size)] = specials[::-1][: bv.size]
+        a, b = Buf(p, av), Buf(p, bv)
+        dense = tuple(contiguous_strides(shape))
+        for code in offered:
+            first, second = FUSED[code]
+            fused, mid, seq = Buf.empty(p, n), Buf.empty(p, n), Buf.empty(p, n)
+            assert exec_op(p, code, [0], [(a, shape, sa), (b, shape, sb)], fused, shape) == abi.STATUS_OK, p.last_error()
+            if code == op.RELU_GRAD:  # MUL(g, STEP(x))
+                assert exec_op(p, op.STEP, [0], [(b, shape, sb)], mid, shape) == abi.STATUS_OK
+                assert exec_op(p, op.MUL, [0], [(a, shape, sa), (mid, shape, dense)], seq, shape) == abi.STATUS_OK
+            else:
+                assert exec_op(p, first, [0], [(a, shape, sa), (b, shape, sb)], mid, shape) == abi.STATUS_OK
+                assert exec_op(p, second, [0], [(mid, shape, dense)], seq, shape) == abi.STATUS_OK
+            assert_bit_equal(f"fused op {code} vs its sequence, {shape} {sa} {sb}", fused.get(), seq.get())
+    # same arity and shape rules as the binary ops
+    x = Buf(p, lcg_data(12, 1))
+    out = Buf.empty(p, 12)
+    for code in offered:
+        assert exec_op(p, code, [0], [(x, (3, 4), (4, 1))], out, (3, 4)) == abi.STATUS_INVALID_ARGUMENT
+        assert exec_op(p, code, [0], [(x, (3, 4), (4, 1)), (x, (4, 3), (3, 1))], out, (3, 4)) == abi.STATUS_INVALID_ARGUMENT
+    # the host uses them only when offered, and gets the same values and gradients either way
+    grads = {}
+    for fused in (True, False):
+        dev = Device(p, 0, fused=fused)
+        A = Tensor.from_numpy(lcg_data(6 * 50, 7).reshape(6, 50), dev, requires_grad=True)
+        bias = Tensor.from_numpy(lcg_data(50, 8).reshape(1, 50), dev, requires_grad=True)
+        m = Tensor.from_numpy(lcg_data(6, 9).reshape(6, 1), dev, requires_grad=True)
+        y = A.add_relu(bias).sub_exp(m).mul(A.relu())
+        loss = y.sum()
+        loss.backward()
+        grads[fused] = [loss.numpy(), A.grad.numpy(), bias.grad.numpy(), m.grad.numpy()]
+    for got, want in zip(grads[True], grads[False]):
+        assert_bit_equal("fused vs unfused host sequences", got.reshape(-1), want.reshape(-1))
+
+
 def check_concurrent_threads(p):
     """docs/plugin-abi.md:228-236: every entry point may be called from any number of threads; calls into
     one device behave as if serialized; last_error is per thread. Eight threads each run their own chain
@@ -466,5 +524,6 @@ ALL_CHECKS = [
     check_zero_sized_and_scalars,
     check_diff_against_torch,
     check_max_argmax_against_torch,
+    check_fused_ops_equal_their_sequences,
     check_concurrent_threads,
 ]

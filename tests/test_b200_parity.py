@@ -89,6 +89,34 @@ def test_binary_ops_bit_exact(oracle, b200, shape, sa, sb):
         assert_bit_equal(f"binary {code} {shape} {sa} {sb}", got, want)
 
 
+@pytest.mark.parametrize("shape,sa,sb", BROADCAST_CASES + [((7,), (1,), (1,)), ((65543,), (1,), (0,)), ((5, 13), (13, 1), (1, 0))])
+def test_fused_ops_bit_exact(oracle, b200, shape, sa, sb):
+    """RELU_GRAD, ADD_RELU, SUB_EXP: the oracle computes them as their two-op sequences; every layout the
+    binary kernels serve must give those bits, the libm-computed last (n mod 8) elements of SUB_EXP within 2 ulp."""
+    a = storage_for(shape, sa, 5)
+    b = storage_for(shape, sb, 6)  # both zero-centred: relu and step see both signs
+    for code in (op.RELU_GRAD, op.ADD_RELU):
+        got, want = both(oracle, b200, code, [0], [(a, shape, sa), (b, shape, sb)], shape)
+        assert_bit_equal(f"fused {code} {shape} {sa} {sb}", got, want)
+    a20 = a * np.float32(20.0)
+    got, want = both(oracle, b200, op.SUB_EXP, [0], [(a20, shape, sa), (b, shape, sb)], shape)
+    n = got.size
+    body = n - n % 8
+    assert_bit_equal(f"SUB_EXP body {shape} {sa} {sb}", got[:body], want[:body])
+    assert int(ulp_distance(got[body:], want[body:]).max(initial=0)) <= 2
+
+
+def test_fused_ops_special_values_bit_exact(oracle, b200):
+    specials = np.array([0.0, -0.0, 1e-45, -1e-45, 1e-38, 1.0, -1.0, 3.4e38, -3.4e38, np.inf, -np.inf, np.nan, 1e-20, 1e20, 88.0, -104.0],
+                        dtype=np.float32)
+    a = np.repeat(specials, specials.size)
+    b = np.tile(specials, specials.size)
+    sh = (a.size,)  # 256 elements: no libm tail
+    for code in (op.RELU_GRAD, op.ADD_RELU, op.SUB_EXP):
+        got, want = both(oracle, b200, code, [0], [(a, sh, (1,)), (b, sh, (1,))], sh)
+        assert_bit_equal(f"fused {code} specials", got, want, zero_sign_matters=code != op.ADD_RELU)
+
+
 def test_binary_special_values_bit_exact(oracle, b200):
     specials = np.array([0.0, -0.0, 1e-45, -1e-45, 1e-38, 1.0, -1.0, 3.4e38, -3.4e38, np.inf, -np.inf, np.nan, 1e-20, 1e20], dtype=np.float32)
     a = np.repeat(specials, specials.size)

@@ -33,13 +33,13 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
     from harness import lcg_data
     from pytorches_b200.abi import Plugin, op
     from pytorches_b200.core import Device, Tensor
-    from pytorches_b200.shard import ShardGroup, split_rows
+    from pytorches_b200.shard import ShardGroup, nccl_options, split_rows
 
     if backend == "nccl":
         import torch
 
         torch.cuda.set_device(rank)
-        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=torch.device("cuda", rank), pg_options=nccl_options())
     else:
         dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
