@@ -214,6 +214,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=nccl_options())
     dev = Device(plugin, local)
     group = ShardGroup(dev, rank, world)
+    # PYTORCHES_B200_PEER_EXCHANGE=1: the per-GPU results are exchanged inside the reduction kernels over
+    # peer memory (one launch per reduction, no collective library on the data path) instead of by NCCL.
+    exchange = "NCCL all-gather of the partials, combined by plugin ops"
+    if world > 1 and os.environ.get("PYTORCHES_B200_PEER_EXCHANGE", "0") == "1":
+        if not group.enable_peer_exchange():
+            raise SystemExit("in-kernel peer exchange could not be set up: " + plugin.last_error())
+        exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
     get_stream = plugin.lib.pytorches_b200_stream
     get_stream.restype, get_stream.argtypes = ctypes.c_void_p, [ctypes.c_uint32]
     stream = torch.cuda.ExternalStream(get_stream(local), device=torch.device("cuda", local))
@@ -356,7 +363,7 @@ def main():
         "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "config 2: full-tensor f32 sum/mean/max/argmax over 2^28 elements (1 GiB) per GPU", "elements_per_gpu": N_ELEMS,
-                   "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s), partials all-gathered over NCCL and combined by plugin ops" if world > 1 else "none",
+                   "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s); exchange: {exchange}" if world > 1 else "none",
                    "l2": "input (1 GiB) is larger than L2 (126 MB); no flush needed", "frac_of_measured_peak": round(value / (peak * world), 4),
                    "frac_of_8TBps": round(value / (8000.0 * world), 4)},
         "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "rank_ms_per_step": [round(v / args.steps, 4) for v in rank_ms],

@@ -63,6 +63,38 @@ uint64_t pytorches_b200_kernel_launches(void);
 int32_t pytorches_b200_sum_noalloc(uint32_t device, const float *x, uint64_t n, float *out, void *stream);
 
 /*
+ * Reductions over a tensor whose rows are split across several GPUs, one process per GPU, with the
+ * exchange of the per-GPU results done INSIDE the reduction kernel over peer memory instead of by a
+ * collective library. The reference has no multi-GPU execution of one op (its planner places whole
+ * layers, crates/core/src/strategy.rs:221-326, and moves tensors through host memory,
+ * crates/core/src/lib.rs:535-542), so these replace nothing in it.
+ *
+ * Each process owns a small "window" of device memory per GPU. pytorches_b200_peer_export creates and
+ * zeroes this device's window and writes its 64-byte CUDA IPC handle to `handle_out`; the host
+ * exchanges the handles between the ranks by whatever means it has (the Python host uses
+ * torch.distributed); pytorches_b200_peer_attach(device, rank, world, handles, wait_ms) then maps the
+ * other ranks' windows (`handles` = world x 64 bytes in rank order, this device's own at index `rank`;
+ * world <= 8; wait_ms = how long a kernel waits for its peers, 0 = 2000).
+ *
+ * pytorches_b200_peer_reduce(device, kind, x, n, first_index, seq, out) enqueues, on the device's
+ * stream, the reduction of this rank's n f32 values at `x` AND the combination with every other
+ * rank's result: kind 0 = sum (f32 to out), 1 = max (f32), 2 = argmax (i64: position in the whole
+ * tensor, `first_index` being where this rank's shard starts in it). The kernel that finishes the
+ * local reduction stores the result with plain peer stores into a slot of EVERY rank's window, waits
+ * (bounded) until its own window holds all ranks' results, combines them in rank order and writes
+ * `out`; every rank ends with the same bits, those the vtable ops give when they combine the gathered
+ * per-rank results (SUM_AXIS / MAX_AXIS / ARGMAX_COMBINE over a [world, ...] tensor).
+ *
+ * `seq` numbers the reductions of the group: every rank must pass the same value for the same
+ * reduction and a different one for the next (a counter). All ranks must call in the same order. If
+ * a peer's result does not arrive within wait_ms the kernel gives up, nothing hangs, and the next
+ * blocking vtable call on the device returns PT_STATUS_INTERNAL once. All return a PtStatus.
+ */
+int32_t pytorches_b200_peer_export(uint32_t device, void *handle_out);
+int32_t pytorches_b200_peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms);
+int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out);
+
+/*
  * Failure-path self test. The staged reduction kernels wait for their asynchronous copies with a
  * bounded number of tries; if a wait ever ran out they would record it in a host-visible status word
  * and the next blocking vtable call (synchronize, copy_to_host) would return PT_STATUS_INTERNAL

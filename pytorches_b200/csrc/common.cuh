@@ -73,9 +73,31 @@ cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const floa
 // SUM and MAX write f32 values to out_v, ARGMAX i64 positions to out_i, MAX_ARGMAX both; positions
 // get idx_offset added (the shard's first row when the axis is split over devices).
 enum ReduceKind : int { REDUCE_SUM = 0, REDUCE_MAX = 1, REDUCE_ARGMAX = 2, REDUCE_MAX_ARGMAX = 3 };
+
+// The cross-GPU step of a reduction whose input is split over several GPUs (one process each): what a
+// kernel needs to hand its GPU's result to every peer and to collect theirs. Every rank owns a small
+// "window" of device memory that all ranks have mapped (CUDA IPC); rank r's result for the reduction
+// numbered `epoch` goes, as plain peer stores over NVLink, into slot r of EVERY rank's window, so that
+// each rank then finds all results in its OWN memory and combines them in rank order. world == 0
+// means "no cross-GPU step".
+constexpr int PEER_MAX_RANKS = 8;
+struct PeerXchg {
+    unsigned long long *window[PEER_MAX_RANKS];  // rank r's window as mapped in this process; [rank] is local memory
+    int world;
+    int rank;
+    uint32_t epoch;          // never 0; the same on every rank for the same reduction
+    uint32_t wait_ms;        // how long to wait for the peers before giving up
+};
+// Window management (one window per device of this process). `handle` is a 64-byte CUDA IPC handle.
+cudaError_t peer_window_export(int device, void *handle, cudaStream_t s);
+cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms);
+bool peer_window_for(int device, uint64_t seq, PeerXchg *px);
+
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
+// With `px` (only for outer == inner == 1): the result written is the combination over all ranks, in
+// rank order, of every rank's result; MAX_ARGMAX then needs both outputs, ARGMAX is not offered.
 cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v,
-                          int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s);
+                          int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px = nullptr);
 // Kernels with bounded device-side waits report an expired wait in a host-visible word; this returns
 // and clears it (0 = nothing happened).
 int take_reduce_status();

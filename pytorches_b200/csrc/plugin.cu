@@ -198,9 +198,16 @@ void free_buf(uint32_t device, void *ptr) {
 // A deferred fault is reported by the next call that can (docs/plugin-abi.md:155-156).
 PtStatus finish_blocking(DeviceState &d, const char *what) {
     cudaError_t e = cudaStreamSynchronize(d.stream);
-    if (e == cudaSuccess && take_reduce_status() != 0) {
-        set_err("b200: %s: a reduction kernel gave up on a bounded device-side wait; its result is invalid", what);
-        return PT_STATUS_INTERNAL;
+    if (e == cudaSuccess) {
+        const int gave_up = take_reduce_status();
+        if (gave_up == 2) {
+            set_err("b200: %s: a sharded reduction waited in vain for a peer GPU's result (bounded device-side wait); its result is invalid", what);
+            return PT_STATUS_INTERNAL;
+        }
+        if (gave_up != 0) {
+            set_err("b200: %s: a reduction kernel gave up on a bounded device-side wait; its result is invalid", what);
+            return PT_STATUS_INTERNAL;
+        }
     }
     if (e == cudaSuccess && d.deferred != cudaSuccess) {
         e = d.deferred;
@@ -579,6 +586,46 @@ PtStatus execute(uint32_t device, uint32_t op, const PtOpAttrs *attrs, const PtT
     }
 }
 
+// ---- reductions over a tensor that is split across GPUs (extension entry points) ----------------------------
+
+PtStatus peer_export(uint32_t device, void *handle) {
+    B200_ENTER(device);
+    cudaError_t e = peer_window_export((int)device, handle, d.stream);
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer window export", e);
+}
+
+PtStatus peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms) {
+    if (!handles || world == 0 || world > (uint32_t)PEER_MAX_RANKS || rank >= world)
+        B200_INVALID("b200: peer attach: rank %u of %u ranks (at most %d)", rank, world, PEER_MAX_RANKS);
+    B200_ENTER(device);
+    cudaError_t e = peer_window_attach((int)device, rank, world, handles, wait_ms);
+    if (e == cudaErrorInvalidValue) B200_INVALID("b200: peer attach: export this device's window first and pass its handle at index `rank`");
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer window attach (CUDA IPC)", e);
+}
+
+PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out) {
+    if (kind > 2) B200_INVALID("b200: peer reduce: kind %u is not 0 (sum), 1 (max) or 2 (argmax)", kind);
+    if (!out || (!x && n)) B200_INVALID("b200: peer reduce: null pointer");
+    if (kind != 0 && n == 0) B200_INVALID("b200: peer reduce: max/argmax of an empty shard has no value");
+    B200_ENTER(device);
+    PeerXchg px;
+    if (!peer_window_for((int)device, seq, &px)) B200_INVALID("b200: peer reduce: no peer windows attached on device %u", device);
+    const ReduceKind rk = kind == 0 ? REDUCE_SUM : kind == 1 ? REDUCE_MAX : REDUCE_MAX_ARGMAX;
+    void *scratch = nullptr, *value = nullptr;
+    const size_t sb = reduce_scratch_bytes(rk, 1, n, 1, (int)device);
+    PtStatus st = PT_STATUS_OK;
+    if (sb && (st = alloc_locked(d, sb, &scratch)) != PT_STATUS_OK) return st;
+    if (kind == 2 && (st = alloc_locked(d, sizeof(float), &value)) != PT_STATUS_OK) {  // the maximum travels with its position
+        if (scratch) free_locked(d, scratch);
+        return st;
+    }
+    cudaError_t e = launch_reduce(rk, x, 1, n, 1, kind == 2 ? (float *)value : (float *)out, kind == 2 ? (int64_t *)out : nullptr, first_index,
+                                  scratch, (int)device, d.stream, &px);
+    if (scratch) free_locked(d, scratch);
+    if (value) free_locked(d, value);
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer reduce", e);
+}
+
 const PtPluginVTable VTABLE = {
     PT_ABI_VERSION, PT_VTABLE_SIZE, 1, "b200",
     device_count, device_info, alloc_buf, free_buf, copy_from_host, copy_to_host, copy_d2d,
@@ -618,5 +665,31 @@ B200_EXPORT void *pytorches_b200_stream(uint32_t device) {
 }
 
 B200_EXPORT uint64_t pytorches_b200_kernel_launches(void) { return b200::g_kernel_launches.load(std::memory_order_relaxed); }
+
+B200_EXPORT int32_t pytorches_b200_peer_export(uint32_t device, void *handle_out) {
+    try {
+        if (!handle_out) return PT_STATUS_INVALID_ARGUMENT;
+        return b200::peer_export(device, handle_out);
+    } catch (...) {
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms) {
+    try {
+        return b200::peer_attach(device, rank, world, handles, wait_ms);
+    } catch (...) {
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq,
+                                               void *out) {
+    try {
+        return b200::peer_reduce(device, kind, x, n, first_index, seq, out);
+    } catch (...) {
+        return PT_STATUS_INTERNAL;
+    }
+}
 
 }  // extern "C"

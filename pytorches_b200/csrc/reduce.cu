@@ -17,7 +17,10 @@
 // All kernels are pure HBM streaming: every load of a thread's batch is issued before the first use.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include <cuda.h>  // CUtensorMap and its enums only; the encoder is looked up at run time, libcuda is not linked
 
@@ -139,11 +142,116 @@ __device__ __forceinline__ unsigned long long ld_mailbox(const unsigned long lon
     return v;
 }
 
+__device__ __forceinline__ bool vi_better(float v, uint64_t i, float bv, uint64_t bi);
+
+// ---- the cross-GPU step --------------------------------------------------------------------------------------
+// Called by one whole warp with the same (v, pos) in every lane: this GPU's result. Lane r < world
+// stores it into slot `rank` of rank r's window (its own window included) and then waits for slot r
+// of its OWN window to be filled by rank r. A slot is two 64-bit words: the position, written first,
+// then (epoch << 32) | float bits, written with release semantics at system scope; the reader polls
+// that word with acquire loads until it carries this reduction's epoch. Four generations of slots are
+// used in turn, so a fast rank's next reduction never lands on a slot a slow rank has yet to read (to
+// run two reductions ahead a rank would need the slow rank's result of the one in between).
+// The wait is bounded in time; if a peer never shows up the warp records it in *status and returns
+// false without a result, and the host reports the failure at its next blocking call.
+constexpr int PEER_GENERATIONS = 4;
+constexpr int PEER_SLOT_WORDS = 2;
+constexpr size_t PEER_WINDOW_WORDS = (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_SLOT_WORDS;
+constexpr int STATUS_PEER_WAIT_EXPIRED = 2;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ bool peer_allgather(const PeerXchg &px, float v, int64_t pos, float &rv, int64_t &rp, int *status) {
+    const int lane = threadIdx.x & 31;
+    const size_t gen = (size_t)(px.epoch % PEER_GENERATIONS) * PEER_MAX_RANKS * PEER_SLOT_WORDS;
+    bool ok = true;
+    rv = 0.0f;
+    rp = 0;
+    // The window table sits in the kernel's parameter space: picked with compares, not indexed, so that it stays there.
+    unsigned long long *to = px.window[0], *mine = px.window[0];
+#pragma unroll
+    for (int r = 1; r < PEER_MAX_RANKS; ++r) {
+        if (lane == r) to = px.window[r];
+        if (px.rank == r) mine = px.window[r];
+    }
+    if (lane < px.world) {
+        unsigned long long *dst = to + gen + (size_t)px.rank * PEER_SLOT_WORDS;
+        const unsigned long long w = ((unsigned long long)px.epoch << 32) | __float_as_uint(v);
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + 1), "l"((unsigned long long)pos) : "memory");
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+        const unsigned long long *src = mine + gen + (size_t)lane * PEER_SLOT_WORDS;
+        const unsigned long long t0 = global_ns(), limit = (unsigned long long)px.wait_ms * 1000000ull;
+        ok = false;
+        for (uint32_t tries = 0; tries < (1u << 30); ++tries) {  // the time limit ends the loop; the count is a second guard
+            unsigned long long got;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+            if ((uint32_t)(got >> 32) == px.epoch) {
+                unsigned long long p2;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(p2) : "l"(src + 1) : "memory");
+                rv = __uint_as_float((uint32_t)got);
+                rp = (int64_t)p2;
+                ok = true;
+                break;
+            }
+            if ((tries & 63) == 63 && global_ns() - t0 > limit) break;
+        }
+    }
+    if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) {
+            *(volatile int *)status = STATUS_PEER_WAIT_EXPIRED;
+            __threadfence_system();
+        }
+        return false;
+    }
+    return true;
+}
+
+// Exchanges this GPU's result with the peers and combines all of them in rank order, exactly as the
+// same plugin op would combine a [world] tensor of the per-rank results: SUM adds them one by one to
+// 0.0 and adds that to 0.0 (the row path for rows shorter than 32, sum_short_rows_kernel); MAX and
+// MAX_ARGMAX keep the best (value, position): NaN wins, then the larger value, then the lower position.
+// Whole warp, same (v, pos) in every lane; lane 0 writes. Returns without writing if the wait expired.
+__device__ void peer_finish(const PeerXchg &px, int kind, float v, int64_t pos, float *out_v, int64_t *out_i, int *status) {
+    const int lane = threadIdx.x & 31;
+    float rv;
+    int64_t rp;
+    if (!peer_allgather(px, v, pos, rv, rp, status)) return;
+    if (kind == REDUCE_SUM) {
+        float s = 0.0f;
+        for (int r = 0; r < px.world; ++r) s = __fadd_rn(s, __shfl_sync(0xffffffffu, rv, r));
+        if (lane == 0) out_v[0] = __fadd_rn(0.0f, s);
+        return;
+    }
+    float bv = lane < px.world ? rv : __int_as_float(0xff800000);
+    uint64_t bp = lane < px.world ? (uint64_t)rp : ~0ull;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+        const uint64_t op = __shfl_xor_sync(0xffffffffu, bp, d);
+        if (vi_better(ov, op, bv, bp)) { bv = ov; bp = op; }
+    }
+    if (lane == 0) {
+        if (out_v) out_v[0] = bv;
+        if (out_i) out_i[0] = (int64_t)bp;
+    }
+}
+
+// The cross-GPU step alone, for reductions whose local part did not end in a combiner CTA (short
+// inputs): reads this GPU's finished result from the output locations and overwrites them.
+__global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant__ PeerXchg px, int kind, float *v, int64_t *i, int *status) {
+    peer_finish(px, kind, v ? v[0] : 0.0f, i ? i[0] : 0, v, i, status);
+}
+
 // A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 256 words
 // per round (8 per lane, all in flight together) and re-polls only the ones not yet published.
 constexpr int COMBINER_WORDS = 8;
 
-__device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status) {
+__device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
+                                 const PeerXchg &px) {
     const int lane = threadIdx.x;
     float s = 0.0f;
     for (uint64_t base = 0; base < blocks; base += 32 * COMBINER_WORDS) {
@@ -186,16 +294,18 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
             }
         }
     }
+    if (px.world > 0) return peer_finish(px, REDUCE_SUM, s, 0, out, nullptr, status);  // s is the same in every lane
     if (lane == 0) out[0] = s;
 }
 
 template <bool FUSED>
 __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
-                                                          float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch) {
+                                                          float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch,
+                                                          const __grid_constant__ PeerXchg px) {
     extern __shared__ __align__(128) unsigned char tma_smem[];
     __shared__ uint64_t bars[TMA_STAGES];
     float *ring = reinterpret_cast<float *>(tma_smem);
-    if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status);
+    if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status, px);
     const uint64_t t = FUSED ? blockIdx.x - 1 : blockIdx.x;
     const int lane = threadIdx.x;
     if (lane == 0) {
@@ -450,7 +560,7 @@ constexpr int MAX_UNROLL = 4;
 // NaN wins, then the larger value, then the lower segment - and writes the row's result. Max is
 // order-free, so all 256 threads poll and scan in parallel; polls are bounded.
 __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v,
-                             int64_t *out_i, int64_t idx_offset, int *status) {
+                             int64_t *out_i, int64_t idx_offset, int *status, const PeerXchg &px) {
     __shared__ float sv[8];
     __shared__ uint64_t ss[8];
     constexpr int WORDS = 8;
@@ -509,6 +619,12 @@ __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, 
             const uint64_t os = __shfl_xor_sync(0xffffffffu, bs, d);
             if (vi_better(ov, os, bv, bs)) { bv = ov; bs = os; }
         }
+        if (px.world > 0) {  // lanes 0-7 hold the row's best pair; hand lane 0's to the whole warp
+            bv = __shfl_sync(0xffffffffu, bv, 0);
+            bs = __shfl_sync(0xffffffffu, bs, 0);
+            const int64_t pos = out_i ? seg_pos[bs] + idx_offset : 0;
+            return peer_finish(px, out_i ? REDUCE_MAX_ARGMAX : REDUCE_MAX, bv, pos, out_v, out_i, status);
+        }
         if (threadIdx.x == 0) {
             if (out_i) out_i[0] = seg_pos[bs] + idx_offset;
             if (out_v) out_v[0] = bv;
@@ -524,6 +640,7 @@ struct MaxFused {
     int64_t *final_i;
     int64_t final_offset;
     int *status;
+    PeerXchg px;
 };
 
 // inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
@@ -533,10 +650,10 @@ struct MaxFused {
 template <int TPT, int VEC, bool ARG>
 __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
                                                            uint64_t segs, uint64_t seg_len, float *__restrict__ out_v,
-                                                           int64_t *__restrict__ out_i, int64_t idx_offset, const MaxFused fused) {
+                                                           int64_t *__restrict__ out_i, int64_t idx_offset, const __grid_constant__ MaxFused fused) {
     constexpr int PER_CTA = MAX_CTA / TPT;
     if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
-        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status);
+        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px);
     const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
     const uint64_t t = cta * PER_CTA + threadIdx.x / TPT;
     const int lane = threadIdx.x % TPT;
@@ -827,6 +944,92 @@ bool make_cols_tensor_map(CUtensorMap *map, const float *x, uint64_t rows, uint6
 }
 }  // namespace
 
+// ---- peer windows ------------------------------------------------------------------------------------------
+// One window per device of this process: a 2 MiB allocation of its own (so that its IPC handle shares
+// a driver allocation with nothing else), of which the first PEER_WINDOW_WORDS words are used. It is
+// created and zeroed by the first export and kept for the life of the process; every export zeroes it
+// again, so that epochs may restart with a new group of ranks. Peers' windows are opened once per
+// handle and never closed.
+namespace {
+constexpr size_t PEER_WINDOW_BYTES = size_t(2) << 20;
+struct PeerWindows {
+    std::mutex mu;
+    unsigned long long *local[64] = {};
+    cudaIpcMemHandle_t local_handle[64] = {};
+    std::vector<std::pair<cudaIpcMemHandle_t, void *>> opened[64];
+    PeerXchg attached[64] = {};
+};
+PeerWindows &peer_windows() {
+    static PeerWindows w;
+    return w;
+}
+}  // namespace
+
+cudaError_t peer_window_export(int device, void *handle, cudaStream_t s) {
+    if (device < 0 || device >= 64 || !handle) return cudaErrorInvalidValue;
+    PeerWindows &w = peer_windows();
+    std::lock_guard<std::mutex> lock(w.mu);
+    cudaError_t e;
+    if (!w.local[device]) {
+        void *p = nullptr;
+        if ((e = cudaMalloc(&p, PEER_WINDOW_BYTES)) != cudaSuccess) return e;
+        if ((e = cudaIpcGetMemHandle(&w.local_handle[device], p)) != cudaSuccess) {
+            (void)cudaFree(p);
+            return e;
+        }
+        w.local[device] = (unsigned long long *)p;
+    }
+    w.attached[device] = PeerXchg{};
+    // Everything this device has in flight finishes before the window is cleared, and the clearing
+    // finishes before the handle leaves this call: no peer can write before it holds the handle.
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(w.local[device], 0, PEER_WINDOW_BYTES, s)) != cudaSuccess) return e;
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return e;
+    std::memcpy(handle, &w.local_handle[device], sizeof(cudaIpcMemHandle_t));
+    return cudaSuccess;
+}
+
+cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms) {
+    if (device < 0 || device >= 64 || !handles || world == 0 || world > (uint32_t)PEER_MAX_RANKS || rank >= world) return cudaErrorInvalidValue;
+    PeerWindows &w = peer_windows();
+    std::lock_guard<std::mutex> lock(w.mu);
+    if (!w.local[device]) return cudaErrorInvalidValue;  // export first
+    PeerXchg px{};
+    px.world = (int)world;
+    px.rank = (int)rank;
+    px.wait_ms = wait_ms ? wait_ms : 2000;
+    for (uint32_t r = 0; r < world; ++r) {
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, (const char *)handles + (size_t)r * sizeof h, sizeof h);
+        if (std::memcmp(&h, &w.local_handle[device], sizeof h) == 0) {  // this device's own window (rank r == rank, normally)
+            px.window[r] = w.local[device];
+            continue;
+        }
+        void *p = nullptr;
+        for (auto &kv : w.opened[device])
+            if (std::memcmp(&kv.first, &h, sizeof h) == 0) p = kv.second;
+        if (!p) {
+            cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) return e;
+            w.opened[device].emplace_back(h, p);
+        }
+        px.window[r] = (unsigned long long *)p;
+    }
+    if (px.window[rank] != w.local[device]) return cudaErrorInvalidValue;  // handles[rank] must be this device's own
+    w.attached[device] = px;
+    return cudaSuccess;
+}
+
+bool peer_window_for(int device, uint64_t seq, PeerXchg *px) {
+    if (device < 0 || device >= 64) return false;
+    PeerWindows &w = peer_windows();
+    std::lock_guard<std::mutex> lock(w.mu);
+    if (w.attached[device].world <= 0) return false;
+    *px = w.attached[device];
+    px->epoch = (uint32_t)(seq % 0xfffffffeull) + 1;
+    return true;
+}
+
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device) {
     if (inner != 1 || outer == 0 || len == 0) return 0;
     if (kind == REDUCE_SUM) {
@@ -840,8 +1043,12 @@ size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint6
     return ((tasks * 4 + 15) & ~15ull) + (kind != REDUCE_MAX ? tasks * 8 : 0);
 }
 
-cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
-                          int64_t idx_offset, void *scratch, int device, cudaStream_t s) {
+namespace {
+// The local reduction. With `px`, a launch that ends in a combiner CTA also does the cross-GPU step
+// there and sets *peer_done; every other path leaves it to the caller.
+cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
+                                int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px, bool *peer_done) {
+    const PeerXchg no_peers{};
     const uint64_t total = outer * inner;
     if (total == 0) return cudaSuccess;
     if (kind == REDUCE_SUM) {
@@ -861,11 +1068,13 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
                 uint32_t epoch = 0;
                 unsigned long long *mailbox = (outer == 1 && blocks >= 64 && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
                 if (mailbox) {
-                    B200_LAUNCH(sum_rows_tma_kernel<true>, (unsigned)tasks + 1, 32, TMA_SMEM, s, x, tasks, len, blocks, o, status, mailbox, epoch);
+                    B200_LAUNCH(sum_rows_tma_kernel<true>, (unsigned)tasks + 1, 32, TMA_SMEM, s, x, tasks, len, blocks, o, status, mailbox, epoch,
+                                px ? *px : no_peers);
+                    *peer_done = px != nullptr;
                     return cudaGetLastError();
                 }
                 B200_LAUNCH(sum_rows_tma_kernel<false>, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status,
-                            (unsigned long long *)nullptr, 0u);
+                            (unsigned long long *)nullptr, 0u, no_peers);
             } else {
                 B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
             }
@@ -917,8 +1126,9 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
         uint32_t epoch = 0;
         unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
         if (mailbox) {
-            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status};
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers};
             grid += 1;
+            *peer_done = px != nullptr;
         }
     }
 #define B200_MAX_CASE(TPT, VEC)                                                                                                              \
@@ -932,6 +1142,20 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
     if (m.segs > 1 && !fused.mailbox) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
+    return cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
+                          int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px) {
+    if (px && (px->world <= 0 || outer != 1 || inner != 1 || kind == REDUCE_ARGMAX || !out_v || (kind == REDUCE_MAX_ARGMAX && !out_i)))
+        return cudaErrorInvalidValue;
+    bool peer_done = false;
+    cudaError_t e = launch_reduce_local(kind, x, outer, len, inner, out_v, out_i, idx_offset, scratch, device, s, px, &peer_done);
+    if (e != cudaSuccess || !px || peer_done) return e;
+    int *status = reduce_status_word();
+    if (!status) return cudaErrorMemoryAllocation;
+    B200_LAUNCH(peer_exchange_kernel, 1, 32, 0, s, *px, (int)kind, out_v, kind == REDUCE_MAX_ARGMAX ? out_i : (int64_t *)nullptr, status);
     return cudaGetLastError();
 }
 

@@ -82,6 +82,8 @@ class ShardGroup:
         self._stream = None
         self._pending: list = []  # combines not yet enqueued: (collectives to wait for, what to enqueue)
         self._views: dict = {}  # (pointer, elements, dtype) -> torch alias; the allocator hands the same blocks out again
+        self._peer_reduce = None  # set by enable_peer_exchange: full-tensor reductions then exchange inside their kernel
+        self._peer_seq = 0
         if self.is_cuda and world > 1:
             fn = device.plugin.lib.pytorches_b200_stream
             fn.restype, fn.argtypes = C.c_void_p, [C.c_uint32]
@@ -91,6 +93,51 @@ class ShardGroup:
             # entering a stream context around every collective (that costs more host time per step
             # than the collectives themselves).
             torch.cuda.set_stream(self._stream)
+
+    # ---- in-kernel exchange over peer memory ----
+    def enable_peer_exchange(self, wait_ms: int = 0) -> bool:
+        """Switches the full-tensor reductions (``sum``, ``mean``, ``max``, ``argmax``) from "local pass,
+        NCCL all-gather, combine op" to ONE launch per reduction: the kernel that finishes the local
+        pass stores this GPU's result into every rank's peer-mapped window over NVLink, waits (bounded:
+        ``wait_ms``, default 2 s) for the other ranks' results to land in its own window and combines
+        them in rank order. Same bits as the NCCL path. Only the B200 plugin has this (its extension
+        entry points ``pytorches_b200_peer_*``); ranks are processes on one node, at most 8. Collective:
+        every rank must call it; returns False (and changes nothing) unless it worked on all of them."""
+        lib = self.device.plugin.lib
+        if not self.is_cuda or not hasattr(lib, "pytorches_b200_peer_reduce") or self.world > 8:
+            ok = False
+        else:
+            export, attach, reduce_ = lib.pytorches_b200_peer_export, lib.pytorches_b200_peer_attach, lib.pytorches_b200_peer_reduce
+            export.restype, export.argtypes = C.c_int32, [C.c_uint32, C.c_void_p]
+            attach.restype, attach.argtypes = C.c_int32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, C.c_uint32]
+            reduce_.restype = C.c_int32
+            reduce_.argtypes = [C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int64, C.c_uint64, C.c_void_p]
+            self.flush()
+            handle = C.create_string_buffer(64)
+            ok = export(self.device.index, handle) == 0
+        mine = handle.raw if ok else b""
+        if self.world > 1:
+            every = [None] * self.world
+            dist.all_gather_object(every, mine, group=self.group)
+        else:
+            every = [mine]
+        ok = all(len(h) == 64 for h in every)
+        if ok:
+            ok = attach(self.device.index, self.rank, self.world, b"".join(every), wait_ms) == 0
+        if self.world > 1:  # all or nothing: a rank that could not map its peers must not leave the others waiting for it
+            flags = [None] * self.world
+            dist.all_gather_object(flags, ok, group=self.group)
+            ok = all(flags)
+        self._peer_reduce, self._peer_seq = (reduce_ if ok else None), 0
+        return ok
+
+    def _peer(self, kind: int, x_local: Tensor, first_index: int = 0) -> Tensor:
+        dev = self.device
+        out = Tensor(Buffer(dev, 1, 8 if kind == 2 else 4), [], dtype=DTYPE_I64 if kind == 2 else DTYPE_F32)
+        seq, self._peer_seq = self._peer_seq, self._peer_seq + 1  # ranks issue the same reductions in the same order
+        dev.plugin.check(self._peer_reduce(dev.index, kind, x_local.buffer.ptr, x_local.numel(), first_index, seq, out.buffer.ptr),
+                         "sharded reduction with in-kernel exchange")
+        return out
 
     # ---- plumbing ----
     def torch_view(self, t: Tensor) -> torch.Tensor:
@@ -171,10 +218,15 @@ class ShardGroup:
 
     def sum(self, x_local: Tensor) -> Tensor:
         """Full-tensor sum: every rank's ``Tensor.sum`` partial, combined in rank order."""
+        if self._peer_reduce:
+            return self._peer(0, x_local)
         return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)], [], DTYPE_F32, self._combine(op.SUM_AXIS))
 
     def mean(self, x_local: Tensor, n_global: int) -> Tensor:
         """``Tensor.mean`` of the reference: the sum, then a DIV by the element count as a scalar tensor."""
+        if self._peer_reduce:
+            return self._peer(0, x_local).raw_binary(Tensor.scalar_on(float(n_global), self.device), op.DIV)
+
         def finish(gathered, out_buf):
             total = gathered[0].raw_sum_axis(0)
             count = Tensor.scalar_on(float(n_global), self.device)
@@ -182,6 +234,8 @@ class ShardGroup:
         return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)], [], DTYPE_F32, finish)
 
     def max(self, x_local: Tensor) -> Tensor:
+        if self._peer_reduce:
+            return self._peer(1, x_local)
         return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_reduce_axis(op.MAX_AXIS, 0)], [], DTYPE_F32,
                            self._combine(op.MAX_AXIS))
 
@@ -189,6 +243,8 @@ class ShardGroup:
         """Position of the maximum in the unsharded flattened tensor; ``first_index`` is where this
         rank's shard starts in it. One pass yields (max, position); the pairs are gathered and the best
         is picked on every rank (NCCL has no pair reduction)."""
+        if self._peer_reduce:
+            return self._peer(2, x_local, first_index)
         dev = self.device
 
         def local_pass():

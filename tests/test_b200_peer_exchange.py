@@ -1,0 +1,66 @@
+"""The in-kernel exchange of sharded reductions, as far as ONE GPU can show it.
+
+Two ranks' kernels that wait for each other must not share a GPU, so the multi-rank exchange itself is
+tested on two GPUs (tests/test_shard_gloo.py, NCCL variant). Here a group of ONE rank runs the same
+code path - the result goes through the window and back - and a group that claims a second rank which
+never writes shows that the wait is bounded and reported, not a hang.
+"""
+
+import numpy as np
+import pytest
+
+from harness import lcg_data
+from pytorches_b200 import abi
+from pytorches_b200.core import Device, Tensor
+from pytorches_b200.shard import ShardGroup
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [1, 5, 1000, 70_001, 1 << 20, (1 << 22) + 3])
+def test_single_rank_group_gives_the_plain_results(b200, n):
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange(), b200.last_error()
+    x = (np.round(lcg_data(n, 9) * 64) / 64).astype(np.float32)
+    x[n // 3] = 7.0
+    x[n - 1] = 7.0
+    t = Tensor.from_numpy(x, dev)
+    bits = lambda a: np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    for _ in range(6):  # more reductions than slot generations
+        assert bits(g.sum(t).numpy()) == bits(t.sum().numpy())
+        assert bits(g.mean(t, n).numpy()) == bits(t.mean().numpy())
+        assert bits(g.max(t).numpy()) == bits(t.max().numpy())
+        assert g.argmax(t, 1000).numpy() == n // 3 + 1000
+
+
+def test_a_peer_that_never_answers_is_a_reported_error_not_a_hang(b200):
+    import ctypes as C
+
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange()
+    # Claim a second rank whose window is this same memory: nothing ever writes rank 1's slot.
+    lib = b200.lib
+    handle = C.create_string_buffer(64)
+    assert lib.pytorches_b200_peer_export(0, handle) == 0
+    assert lib.pytorches_b200_peer_attach(0, 0, 2, handle.raw + handle.raw, 50) == 0  # give up after 50 ms
+    t = Tensor.from_numpy(lcg_data(1 << 20, 3), dev)
+    out = g.sum(t)  # enqueued; the kernel waits 50 ms, records the failure and returns
+    with pytest.raises(abi.PluginError) as err:
+        b200.synchronize(0)
+    assert err.value.status == abi.STATUS_INTERNAL and "peer" in str(err.value)
+    b200.synchronize(0)  # reported once; the device is usable
+    assert g.enable_peer_exchange()  # a fresh one-rank group works again
+    assert g.sum(t).numpy() == t.sum().numpy()
+    del out
+
+
+def test_peer_reduce_needs_attached_windows(b200):
+    import ctypes as C
+
+    lib = b200.lib
+    fn = lib.pytorches_b200_peer_attach
+    fn.restype, fn.argtypes = C.c_int32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, C.c_uint32]
+    assert fn(0, 3, 2, b"\0" * 128, 0) == abi.STATUS_INVALID_ARGUMENT  # rank outside the group
+    assert fn(0, 0, 9, b"\0" * 64 * 9, 0) == abi.STATUS_INVALID_ARGUMENT  # more ranks than a window has slots

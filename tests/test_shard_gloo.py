@@ -85,6 +85,19 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
         dist.all_gather_object(gathered, (got_sum.tobytes(), got_mean.tobytes()))
         assert all(item == gathered[0] for item in gathered)
 
+        # ---- the same reductions with the exchange inside the kernels, over peer memory (B200 plugin only) ----
+        if backend == "nccl":
+            assert g.enable_peer_exchange(), gdev.plugin.last_error()
+            for _ in range(3):  # several in a row: slot generations, epochs
+                assert bits(g.sum(local).numpy()) == bits(want_sum)
+                assert bits(g.mean(local, n).numpy()) == bits(np.float32(want_sum) / np.float32(n))
+                assert bits(g.max(local).numpy()) == bits(full.max().numpy())
+                assert g.argmax(local, start).numpy() == n // 2
+            small = Tensor.from_numpy(x[start:start + 5], gdev)  # a shard too short for a combiner CTA: separate exchange launch
+            want_small = sum((x[split_rows(n, r, world)[0]:][:5].astype(np.float64).sum() for r in range(world)))
+            assert abs(float(g.sum(small).numpy()) - want_small) < 1e-4
+            g._peer_reduce = None  # back to NCCL for what follows
+
         # ---- a [rows, cols] problem: elementwise on shards, then a column sum across shards ----
         rows, cols = 37, 24
         A = lcg_data(rows * cols, 1).reshape(rows, cols)
