@@ -165,7 +165,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 
-__device__ bool peer_allgather(const PeerXchg &px, float v, int64_t pos, float &rv, int64_t &rp, int *status) {
+__device__ __forceinline__ bool peer_allgather(const PeerXchg &px, float v, int64_t pos, float &rv, int64_t &rp, int *status) {
     const int lane = threadIdx.x & 31;
     const size_t gen = (size_t)(px.epoch % PEER_GENERATIONS) * PEER_MAX_RANKS * PEER_SLOT_WORDS;
     bool ok = true;
@@ -215,7 +215,7 @@ __device__ bool peer_allgather(const PeerXchg &px, float v, int64_t pos, float &
 // 0.0 and adds that to 0.0 (the row path for rows shorter than 32, sum_short_rows_kernel); MAX and
 // MAX_ARGMAX keep the best (value, position): NaN wins, then the larger value, then the lower position.
 // Whole warp, same (v, pos) in every lane; lane 0 writes. Returns without writing if the wait expired.
-__device__ void peer_finish(const PeerXchg &px, int kind, float v, int64_t pos, float *out_v, int64_t *out_i, int *status) {
+__device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float v, int64_t pos, float *out_v, int64_t *out_i, int *status) {
     const int lane = threadIdx.x & 31;
     float rv;
     int64_t rp;
