@@ -214,13 +214,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=nccl_options())
     dev = Device(plugin, local)
     group = ShardGroup(dev, rank, world)
-    # PYTORCHES_B200_PEER_EXCHANGE=1: the per-GPU results are exchanged inside the reduction kernels over
-    # peer memory (one launch per reduction, no collective library on the data path) instead of by NCCL.
     exchange = "NCCL all-gather of the partials, combined by plugin ops"
-    if world > 1 and os.environ.get("PYTORCHES_B200_PEER_EXCHANGE", "0") == "1":
-        if not group.enable_peer_exchange():
-            raise SystemExit("in-kernel peer exchange could not be set up: " + plugin.last_error())
-        exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
     get_stream = plugin.lib.pytorches_b200_stream
     get_stream.restype, get_stream.argtypes = ctypes.c_void_p, [ctypes.c_uint32]
     stream = torch.cuda.ExternalStream(get_stream(local), device=torch.device("cuda", local))
@@ -253,6 +247,27 @@ def main():
         tol = 1e-5 * 28 * np.abs(host_np).astype(np.float64).sum()
         assert abs(float(res[0]) - ref_sum) <= tol, (res[0], ref_sum)
         assert float(res[2]) == float(host_np.max()) and int(res[3]) == int(host_np.argmax()), "max/argmax mismatch"
+
+    # ---- N > 1: move the exchange into the reduction kernels (peer stores over NVLink, one launch per
+    # reduction, no collective library on the data path) if it sets up on every rank AND reproduces the
+    # NCCL path's results bit for bit here; otherwise stay on NCCL. PYTORCHES_B200_PEER_EXCHANGE=0 keeps NCCL. ----
+    if world > 1 and os.environ.get("PYTORCHES_B200_PEER_EXCHANGE", "1") != "0":
+        ok = group.enable_peer_exchange()
+        if ok:
+            try:
+                again = [r.numpy() for r in step(x)]
+                ok = all(a.tobytes() == b.tobytes() for a, b in zip(again, res))
+            except Exception as e:  # a bounded wait ran out, or the call failed: the device stays usable
+                print(f"rank {rank}: in-kernel exchange failed its check: {e}", file=sys.stderr)
+                ok = False
+            flags = [None] * world
+            dist.all_gather_object(flags, ok)
+            ok = all(flags)
+        if ok:
+            exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
+        else:
+            group._peer_reduce = None
+            print(f"rank {rank}: staying on the NCCL exchange", file=sys.stderr)
 
     # ---- timed region: K steps, device-resident input ----
     for _ in range(args.warmup):
