@@ -33,5 +33,13 @@ def load_plugin() -> Plugin:
             raise RuntimeError(
                 f"{path} is missing: build it with `python -m pytorches_b200.build` "
                 "(there is no CPU or PyTorch fallback for this plugin)")
+        stamp = os.path.join(os.path.dirname(path), "pytorches_plugin_b200.built_from")
+        if os.path.exists(stamp):  # written by the build: the digest of the sources the library came from
+            from .build import source_digest
+
+            with open(stamp) as f:
+                if f.read().strip() != source_digest():
+                    raise RuntimeError(f"{path} was built from other sources than the ones beside it: "
+                                       "rebuild it with `python -m pytorches_b200.build`")
         _PLUGIN = Plugin(path)
     return _PLUGIN

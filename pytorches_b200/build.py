@@ -41,6 +41,23 @@ def nvcc() -> str:
     return exe
 
 
+STAMP = os.path.join(CSRC, "pytorches_plugin_b200.built_from")
+
+
+def source_digest() -> str:
+    """SHA-256 over everything the library is compiled from (sources, headers, flags). ``build`` records
+    it beside the library and ``pytorches_b200.load_plugin`` refuses a library whose record differs
+    from the sources next to it: a stale build would otherwise be measured and tested in their place."""
+    import hashlib
+
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    hdrs = [x if os.path.isabs(x) else os.path.join(CSRC, x) for x in HEADERS]
+    for path in [os.path.join(CSRC, x) for x in SOURCES] + hdrs:
+        with open(path, "rb") as f:
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
+    return h.hexdigest()
+
+
 def _stale(target: str, deps: list[str]) -> bool:
     if not os.path.exists(target):
         return True
@@ -77,6 +94,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with open(MANIFEST, "w") as f:
         json.dump({"name": "b200", "vendor": "nvidia", "abi": 4, "os": "linux", "arch": "x86_64"}, f, indent=2)
         f.write("\n")
+    with open(STAMP, "w") as f:
+        f.write(source_digest() + "\n")
     return OUT
 
 

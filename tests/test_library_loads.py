@@ -70,3 +70,19 @@ def test_manifest_matches(built):
 
     m = json.load(open(os.path.join(os.path.dirname(built), "pytorches_plugin_b200.json")))
     assert m["name"] == "b200" and m["abi"] == abi.ABI_VERSION
+
+
+def test_a_library_built_from_other_sources_is_refused(built, monkeypatch):
+    """The build records a digest of its sources beside the library; a library whose record does not match
+    the sources next to it (somebody edited a kernel and forgot to rebuild) must not be loaded silently."""
+    import pytorches_b200.build as build
+
+    stamp = os.path.join(os.path.dirname(built), "pytorches_plugin_b200.built_from")
+    if not os.path.exists(stamp):
+        build.build()
+    monkeypatch.setattr(pytorches_b200, "_PLUGIN", None)
+    assert pytorches_b200.load_plugin().name == "b200"
+    monkeypatch.setattr(pytorches_b200, "_PLUGIN", None)
+    monkeypatch.setattr(build, "source_digest", lambda: "0" * 64)
+    with pytest.raises(RuntimeError, match="rebuild"):
+        pytorches_b200.load_plugin()
