@@ -112,6 +112,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--peer", action="store_true",
+                    help="sharded runs: exchange the per-GPU results inside the reduction kernels over peer memory instead of NCCL")
     ap.add_argument("--peak", type=float, default=6454.6, help="HBM GB/s the fraction is quoted against")
     args = ap.parse_args()
 
@@ -133,6 +135,8 @@ def main():
         torch.cuda.set_device(args.device)
         dist.init_process_group("nccl", device_id=torch.device("cuda", args.device), pg_options=nccl_options())
         group = ShardGroup(dev, rank, world)
+        if args.peer and not group.enable_peer_exchange():
+            raise SystemExit("in-kernel peer exchange could not be set up: " + plugin.last_error())
     get_stream = plugin.lib.pytorches_b200_stream
     get_stream.restype, get_stream.argtypes = ctypes.c_void_p, [ctypes.c_uint32]
     torch.cuda.set_device(args.device)
