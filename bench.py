@@ -181,7 +181,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="time budget of the cpu_baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="how long the cpu_baseline leg may run")
     ap.add_argument("--e2e-steps", type=int, default=5)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

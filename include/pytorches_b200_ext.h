@@ -36,7 +36,7 @@ uint64_t pytorches_b200_kernel_launches(void);
  * Sum of the n f32 values at `x` into `out[0]`, for hosts that cannot allocate device memory when
  * they call: a process that handed the whole GPU to its own memory pool at start-up (a serving
  * process, another framework's caching allocator) has nothing left for a library to allocate from,
- * and a host with a latency budget may forbid allocator calls on its hot path because they can stall
+ * and a host with a latency bound may forbid allocator calls on its hot path because they can stall
  * every stream of the device. The vtable's SUM_AXIS takes its inter-pass scratch from the plugin's
  * allocator; this entry point keeps that scratch in a fixed 256 KiB array inside the library
  * instead (every GPU that loads the library holds the array until the process exits) and calls no
