@@ -270,30 +270,59 @@ def main():
             print(f"rank {rank}: staying on the NCCL exchange", file=sys.stderr)
 
     # ---- timed region: K steps, device-resident input ----
-    for _ in range(args.warmup):
-        step(x)
-    barrier()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    op_ev = []  # per-op event pairs for the SUM_AXIS launch (first op of each step)
-    l0 = launches()
-    with ClockSampler(local) as clocks:
-        ev[0].record(stream)
-        t_host = time.perf_counter()
-        for k in range(args.steps):
-            if world == 1:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                s = x.sum()
-                e1.record(stream)
-                op_ev.append((e0, e1))
-                r = [s, x.mean(), x.max(), x.argmax()]
-            else:
-                r = step(x)
-        group.flush()  # combines still deferred behind the last local pass
-        ev[1].record(stream)
-        host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps  # time the host needs to ENQUEUE one step
-        barrier()
-    l1 = launches()
+    def timed_region():
+        """Warm-up, then K timed steps. Returns None if a step failed or the last step's results are not
+        the gate's (possible only with the in-kernel exchange: a peer wait that ran out)."""
+        try:
+            for _ in range(args.warmup):
+                step(x)
+            barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            op_ev = []  # per-op event pairs for the SUM_AXIS launch (first op of each step)
+            l0 = launches()
+            with ClockSampler(local) as clocks:
+                ev[0].record(stream)
+                t_host = time.perf_counter()
+                for k in range(args.steps):
+                    if world == 1:
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        s = x.sum()
+                        e1.record(stream)
+                        op_ev.append((e0, e1))
+                        r = [s, x.mean(), x.max(), x.argmax()]
+                    else:
+                        r = step(x)
+                group.flush()  # combines still deferred behind the last local pass
+                ev[1].record(stream)
+                host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps  # time the host needs to ENQUEUE one step
+                barrier()
+            l1 = launches()
+            same = all(a.numpy().tobytes() == b.tobytes() for a, b in zip(r, res))  # after the timed region: the steps computed the gate's values
+            return (ev, op_ev, l0, l1, clocks, host_ms) if same else None
+        except pytorches_b200.abi.PluginError as e:
+            print(f"rank {rank}: timed region failed: {e}", file=sys.stderr)
+            return None
+
+    timed = timed_region()
+    if world > 1:
+        flags = [None] * world
+        dist.all_gather_object(flags, timed is not None)
+        if not all(flags) and group._peer_reduce is not None:  # every rank goes back to NCCL together and measures again
+            print(f"rank {rank}: in-kernel exchange failed during the timed region; measuring with NCCL", file=sys.stderr)
+            group._peer_reduce = None
+            exchange = "NCCL all-gather of the partials, combined by plugin ops (the in-kernel exchange failed in this run)"
+            try:
+                dev.synchronize()
+            except pytorches_b200.abi.PluginError:
+                pass  # the deferred report of the failed wait, if this rank had not seen it yet
+            timed = timed_region()
+            dist.all_gather_object(flags, timed is not None)
+        if not all(flags):
+            raise SystemExit("the timed steps failed or did not reproduce the gate's results")
+    elif timed is None:
+        raise SystemExit("the timed steps failed or did not reproduce the gate's results")
+    ev, op_ev, l0, l1, clocks, host_ms = timed
     ms = ev[0].elapsed_time(ev[1])
     t_ms = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
     rank_ms = [ms]
