@@ -243,7 +243,7 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
 // The cross-GPU step alone, for reductions whose local part did not end in a combiner CTA (short
 // inputs): reads this GPU's finished result from the output locations and overwrites them.
 __global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant__ PeerXchg px, int kind, float *v, int64_t *i, int *status) {
-    peer_finish(px, kind, v ? v[0] : 0.0f, i ? i[0] : 0, v, i, status);
+    peer_finish(px, kind, v ? v[0] : 0.0f, i ? i[0] : (int64_t)px.rank, v, i, status);  // no position: the rank breaks ties
 }
 
 // A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 256 words
@@ -622,7 +622,9 @@ __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, 
         if (px.world > 0) {  // lanes 0-7 hold the row's best pair; hand lane 0's to the whole warp
             bv = __shfl_sync(0xffffffffu, bv, 0);
             bs = __shfl_sync(0xffffffffu, bs, 0);
-            const int64_t pos = out_i ? seg_pos[bs] + idx_offset : 0;
+            // Without positions, the rank stands in for one: equal maxima (+0 and -0, two NaNs) then resolve
+            // to the lower rank, as a scan over the per-rank results in rank order would.
+            const int64_t pos = out_i ? seg_pos[bs] + idx_offset : (int64_t)px.rank;
             return peer_finish(px, out_i ? REDUCE_MAX_ARGMAX : REDUCE_MAX, bv, pos, out_v, out_i, status);
         }
         if (threadIdx.x == 0) {
