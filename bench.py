@@ -276,11 +276,14 @@ def main():
         try:
             for _ in range(args.warmup):
                 step(x)
-            barrier()
+            # Everything slow or uneven between ranks (NVML start-up, allocations of events) happens BEFORE the
+            # barrier: a rank that starts its first timed reduction late makes every other rank wait for it there.
+            sampler = ClockSampler(local)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             op_ev = []  # per-op event pairs for the SUM_AXIS launch (first op of each step)
             l0 = launches()
-            with ClockSampler(local) as clocks:
+            barrier()
+            with sampler as clocks:
                 ev[0].record(stream)
                 t_host = time.perf_counter()
                 for k in range(args.steps):
