@@ -266,7 +266,7 @@ def main():
         if ok:
             exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
         else:
-            group._peer_reduce = None
+            group.disable_peer_exchange()
             print(f"rank {rank}: staying on the NCCL exchange", file=sys.stderr)
 
     # ---- timed region: K steps, device-resident input ----
@@ -311,9 +311,9 @@ def main():
     if world > 1:
         flags = [None] * world
         dist.all_gather_object(flags, timed is not None)
-        if not all(flags) and group._peer_reduce is not None:  # every rank goes back to NCCL together and measures again
+        if not all(flags) and group.peer_exchange:  # every rank goes back to NCCL together and measures again
             print(f"rank {rank}: in-kernel exchange failed during the timed region; measuring with NCCL", file=sys.stderr)
-            group._peer_reduce = None
+            group.disable_peer_exchange()
             exchange = "NCCL all-gather of the partials, combined by plugin ops (the in-kernel exchange failed in this run)"
             try:
                 dev.synchronize()

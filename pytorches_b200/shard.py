@@ -131,6 +131,14 @@ class ShardGroup:
         self._peer_reduce, self._peer_seq = (reduce_ if ok else None), 0
         return ok
 
+    def disable_peer_exchange(self) -> None:
+        """Back to the NCCL exchange (every rank must do the same before its next reduction)."""
+        self._peer_reduce = None
+
+    @property
+    def peer_exchange(self) -> bool:
+        return self._peer_reduce is not None
+
     def _peer(self, kind: int, x_local: Tensor, first_index: int = 0) -> Tensor:
         dev = self.device
         out = Tensor(Buffer(dev, 1, 8 if kind == 2 else 4), [], dtype=DTYPE_I64 if kind == 2 else DTYPE_F32)

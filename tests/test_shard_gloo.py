@@ -96,7 +96,7 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
             small = Tensor.from_numpy(x[start:start + 5], gdev)  # a shard too short for a combiner CTA: separate exchange launch
             want_small = sum((x[split_rows(n, r, world)[0]:][:5].astype(np.float64).sum() for r in range(world)))
             assert abs(float(g.sum(small).numpy()) - want_small) < 1e-4
-            g._peer_reduce = None  # back to NCCL for what follows
+            g.disable_peer_exchange()  # back to NCCL for what follows
 
         # ---- a [rows, cols] problem: elementwise on shards, then a column sum across shards ----
         rows, cols = 37, 24
