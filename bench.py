@@ -1,12 +1,21 @@
 """Benchmark of the hot path: full-tensor f32 reductions through the plugin's C ABI.
 
-Workload (the configuration the headline metric is quoted on): x = 2^28 f32 elements (1 GiB) per
-GPU, uniform[-1, 1) from a counter hash with seed 7; one step = sum, mean, max and argmax (i64) of
-x, each as the reference core would issue it (``Tensor::sum`` = reshape + SUM_AXIS, ``mean`` = that
-plus a DIV by a scalar tensor). With N > 1 GPUs (one process per GPU) every rank holds its own
-2^28-element shard of a 2^28*N-element tensor (weak scaling) and each op ends with the cross-GPU
-combine of ``pytorches_b200.shard`` (all-gather of per-rank partials over NCCL, combined by plugin
-ops). Algorithmic bytes: 4*n per op, so 4 GiB per step per GPU.
+Workload (the configuration the headline metric is quoted on): ONE tensor x of 2^28 f32 elements
+(1 GiB), uniform[-1, 1) from the ABI's counter hash with seed 7; one step = sum, mean, max and argmax
+(i64) of x, each as the reference core would issue it (``Tensor::sum`` = reshape + SUM_AXIS, ``mean`` =
+that plus a DIV by a scalar tensor). With N > 1 GPUs (one process per GPU) the SAME tensor is split along
+dim 0: rank r holds elements [r * 2^28/N, (r+1) * 2^28/N) (strong scaling), reduces its shard, and each
+op ends with the cross-GPU combine of ``pytorches_b200.shard``, so every N computes the reductions of the
+same 2^28 values. Algorithmic bytes: 4*n per op, 4 GiB per step for the whole job.
+
+A shard of 2^28/N elements approaches the size of L2 (126 MB) at N = 8, so every rank keeps K copies
+of its shard (K * shard >= 512 MiB) and consecutive ops read consecutive copies: an op never finds its
+input in L2.
+
+The timed region is driven by native code: one step is run once through the Python mirror of the
+reference core, its plugin calls (alloc, execute, free, sharded reductions) are written down, and the
+list is replayed through ``pytorches_b200_replay``, as a native host like the reference's core would
+issue it. The Python mirror needs 10-25 us per op, as long as an op runs for on a 128 MiB shard.
 
 Prints ONE JSON line. ``value`` is device-resident throughput (CUDA events on the plugin's stream,
 max over ranks); ``e2e`` is the same step fed from pinned host memory through ``copy_from_host`` with
@@ -22,6 +31,7 @@ from __future__ import annotations
 import argparse
 import ctypes
 import json
+import math
 import os
 import statistics
 import sys
@@ -34,34 +44,29 @@ if ROOT not in sys.path:
 
 import numpy as np
 
+from pytorches_b200.synth import uniform_pm1
+
 N_ELEMS = 1 << 28
 OPS = ("sum", "mean", "max", "argmax")
 ORACLE_SO = os.path.join(ROOT, "oracle", "_build", "pytorches_plugin_cpuref.so")
 METRIC = "f32 elementwise/reduce HBM GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of sum_rows_tma_kernel from the ncu capture summarised in
-# profiles/sum_rows_tma_kernel_256mib.md (2^26 elements: 268.495 MB read, 5.07 MB written back from L2),
-# read part scaled by 4 to this workload's 2^28 elements, write part kept.
-NCU_TRAFFIC_PER_LAUNCH = int(268.495e6 * 4 + 5.07e6)
+ROTATE_BYTES = 512 << 20  # an op's input was last touched at least this many bytes of traffic ago
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused SUM_AXIS launch, from an ncu capture of a
+# 2^26-element launch (268.495 MB read, 5.07 MB written back from L2): the read part grows with the
+# element count and is scaled to this workload's launch, the write part is kept.
+NCU_READ_BYTES_PER_ELEMENT = 268.495e6 / (1 << 26)
+NCU_WRITE_BYTES_PER_LAUNCH = 5.07e6
 
 
-def uniform_pm1(n: int, seed: int, out: np.ndarray | None = None, first: int = 0) -> np.ndarray:
-    """uniform[-1, 1) for counters first..first+n: u = (splitmix64(seed ^ i*GOLDEN) >> 40) / 2^24, value =
-    2u - 1 (the counter hash of the ABI's RAND_NORMAL, crates/plugin-abi/src/lib.rs:101-107). Generated in
-    slices to bound memory."""
-    out = np.empty(n, dtype=np.float32) if out is None else out
-    G = np.uint64(0x9E3779B97F4A7C15)
-    step = 1 << 24
-    with np.errstate(over="ignore"):
-        for lo in range(0, n, step):
-            i = np.arange(lo, min(lo + step, n), dtype=np.uint64) + np.uint64(first)
-            x = np.uint64(seed) ^ (i * G)
-            x = x + G
-            x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
-            x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
-            x = x ^ (x >> np.uint64(31))
-            u = (x >> np.uint64(40)).astype(np.float32) / np.float32(16777216.0)
-            out[lo:lo + i.size] = np.float32(2.0) * u - np.float32(1.0)
-    return out
+def workload_config(world: int) -> dict:
+    """The ``config`` object, the same in both arms (the reference arm runs on this arm's config)."""
+    return {
+        "workload": "config 2: full-tensor f32 sum/mean/max/argmax over ONE tensor of 2^28 elements (1 GiB), uniform[-1,1) seed 7",
+        "elements": N_ELEMS, "ops": list(OPS),
+        "sharding": "none" if world == 1 else f"dim 0 over {world} GPUs, 2^28/{world} elements per GPU, partials combined across GPUs",
+        "l2": "device arm: consecutive ops read consecutive copies of the (shard of the) tensor, copies x size >= 512 MiB, so no op finds "
+              "its input in the 126 MB L2; at 1 and 2 GPUs the input itself is larger than L2",
+    }
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -166,13 +171,44 @@ def reference_arm(args):
     sample = f"full workload (sum, mean, max, argmax over 2^28 f32), {steps} steps on {cores} host threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 2: full-tensor f32 sum/mean/max/argmax over 2^28 elements (1 GiB)", "elements": N_ELEMS,
-                   "ops": list(OPS), "note": "C++ restatement of the reference's Rust CPU plugin (the reference cannot be built on this box)"},
+        "warmup": args.warmup, "ms_per_step": round(per_step * 1e3, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
+        "note": "C++ restatement of the reference's Rust CPU plugin (the reference cannot be built on this box); host cores only, whatever --gpus says",
         "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def host_reference(shard: np.ndarray, first: int) -> dict:
+    """This rank's share of an independent check, from the host copy of its shard: f64 sum and sum of
+    magnitudes, the maximum and the first global position where it occurs."""
+    return {"sum": float(shard.sum(dtype=np.float64)), "abs": float(np.abs(shard).sum(dtype=np.float64)), "max": float(shard.max()),
+            "argmax": first + int(shard.argmax())}
+
+
+def check_against_host(res, parts: list[dict]) -> None:
+    """Device results of the WHOLE tensor against the per-rank host values: sum and mean within the
+    stated tolerance (relative 1e-5 * log2 n of the sum of magnitudes), max and argmax exactly (the lowest
+    global position among equal maxima)."""
+    total, mag = sum(p["sum"] for p in parts), sum(p["abs"] for p in parts)
+    tol = 1e-5 * math.log2(N_ELEMS) * mag
+    best = max(p["max"] for p in parts)
+    where = min(p["argmax"] for p in parts if p["max"] == best)
+    assert abs(float(res[0]) - total) <= tol, ("sum", float(res[0]), total, tol)
+    assert abs(float(res[1]) - total / N_ELEMS) <= tol / N_ELEMS, ("mean", float(res[1]), total / N_ELEMS)
+    assert float(res[2]) == best, ("max", float(res[2]), best)
+    assert int(res[3]) == where, ("argmax", int(res[3]), where)
+
+
+def oracle_shard_sum(shard: np.ndarray):
+    """The CPU oracle's SUM_AXIS of this rank's shard (None if the oracle has not been built). Checker only."""
+    if not os.path.exists(ORACLE_SO):
+        return None
+    from pytorches_b200.abi import Plugin
+    from pytorches_b200.core import Device, Tensor
+
+    dev = Device(Plugin(ORACLE_SO), 0)
+    return Tensor.from_numpy(shard, dev).sum().numpy().reshape(())
 
 
 def main():
@@ -183,6 +219,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="how long the cpu_baseline leg may run")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--min-seconds", type=float, default=0.5, help="the timed region repeats the K steps until it lasts at least this long")
+    ap.add_argument("--warmup-seconds", type=float, default=1.0, help="warm-up continues until this much time has passed")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -199,6 +237,7 @@ def main():
 
     import pytorches_b200
     from pytorches_b200.core import Device, Tensor
+    from pytorches_b200.replay import Recorder
     from pytorches_b200.shard import ShardGroup, nccl_options
 
     rank = int(os.environ.get("RANK", "0"))
@@ -206,13 +245,29 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch one process per GPU (torch.distributed.run)")
+    if N_ELEMS % world:
+        raise SystemExit(f"2^28 elements do not split evenly over {world} GPUs")
     plugin = pytorches_b200.load_plugin()
     if plugin.device_count() <= local:
         raise SystemExit(f"the B200 plugin sees {plugin.device_count()} device(s); rank needs device {local} (there is no CPU fallback)")
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=nccl_options())
-    dev = Device(plugin, local)
+    try:
+        line = run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder, ShardGroup)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+    if line is not None:
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
+
+
+def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder, ShardGroup):
+    import pytorches_b200
+
+    recorder = Recorder(plugin)
+    dev = Device(recorder, local)
     group = ShardGroup(dev, rank, world)
     exchange = "NCCL all-gather of the partials, combined by plugin ops"
     get_stream = plugin.lib.pytorches_b200_stream
@@ -221,18 +276,22 @@ def main():
     launches = plugin.lib.pytorches_b200_kernel_launches
     launches.restype = ctypes.c_uint64
 
-    # This rank's shard: elements [rank*2^28, (rank+1)*2^28) of the global tensor, in pinned host memory.
-    n_global = N_ELEMS * world
-    host = torch.empty(N_ELEMS, dtype=torch.float32, pin_memory=True)
+    # This rank's shard of THE tensor: counters [first, first + n_local) of the seed-7 stream, in pinned host memory.
+    n_local = N_ELEMS // world
+    first = rank * n_local
+    host = torch.empty(n_local, dtype=torch.float32, pin_memory=True)
     host_np = host.numpy()
-    uniform_pm1(N_ELEMS, 7, host_np, first=rank * N_ELEMS)
-    x = Tensor.from_numpy(host_np, dev)
-    first = rank * N_ELEMS
+    uniform_pm1(n_local, 7, host_np, first=first)
+    copies = max(1, -(-ROTATE_BYTES // (4 * n_local)))
+    xs = [Tensor.from_numpy(host_np, dev) for _ in range(copies)]
 
-    def step(t):
+    def step(pick):
+        """One step; ``pick(j)`` is the tensor op j reads (the same values in every copy)."""
         if world == 1:
-            return [t.sum(), t.mean(), t.max(), t.argmax()]
-        return [group.sum(t), group.mean(t, n_global), group.max(t), group.argmax(t, first)]
+            return [pick(0).sum(), pick(1).mean(), pick(2).max(), pick(3).argmax()]
+        return [group.sum(pick(0)), group.mean(pick(1), N_ELEMS), group.max(pick(2)), group.argmax(pick(3), first)]
+
+    rotating = lambda j: xs[j % copies]
 
     def barrier():
         if world > 1:
@@ -240,13 +299,32 @@ def main():
         torch.cuda.synchronize()
         dev.synchronize()
 
-    # ---- correctness gate before any timing: x's reductions against numpy on the host copy ----
-    res = [r.numpy() for r in step(x)]
-    if world == 1:
-        ref_sum = host_np.astype(np.float64).sum()
-        tol = 1e-5 * 28 * np.abs(host_np).astype(np.float64).sum()
-        assert abs(float(res[0]) - ref_sum) <= tol, (res[0], ref_sum)
-        assert float(res[2]) == float(host_np.max()) and int(res[3]) == int(host_np.argmax()), "max/argmax mismatch"
+    def gather(obj):
+        if world == 1:
+            return [obj]
+        every = [None] * world
+        dist.all_gather_object(every, obj)
+        return every
+
+    # ---- correctness gate before any timing, at every N: the device's results for the whole tensor against
+    # (a) numpy in f64 on the host shards and (b) the CPU oracle's per-shard sums combined in rank order ----
+    parts = gather(host_reference(host_np, first))
+    res = [r.numpy() for r in step(rotating)]
+    check_against_host(res, parts)
+    checks = {"vs_host_f64": True}
+    mine = oracle_shard_sum(host_np)
+    shard_sums = gather(None if mine is None else float(mine))
+    if all(s is not None for s in shard_sums):
+        if world == 1:
+            want = np.float32(shard_sums[0])
+        else:  # SUM_AXIS over the [world] tensor of per-rank sums: added one by one to 0.0, then 0.0 + that
+            acc = np.float32(0.0)
+            for s in shard_sums:
+                acc = np.float32(acc + np.float32(s))
+            want = np.float32(np.float32(0.0) + acc)
+        assert np.float32(res[0]).tobytes() == want.tobytes(), ("sum differs from the oracle's rank-ordered combine", float(res[0]), float(want))
+        assert np.float32(res[1]).tobytes() == np.float32(want / np.float32(N_ELEMS)).tobytes(), "mean differs from the oracle's"
+        checks["sum_mean_bit_equal_to_oracle_rank_ordered"] = True
 
     # ---- N > 1: move the exchange into the reduction kernels (peer stores over NVLink, one launch per
     # reduction, no collective library on the data path) if it sets up on every rank AND reproduces the
@@ -255,78 +333,112 @@ def main():
         ok = group.enable_peer_exchange()
         if ok:
             try:
-                again = [r.numpy() for r in step(x)]
+                again = [r.numpy() for r in step(rotating)]
                 ok = all(a.tobytes() == b.tobytes() for a, b in zip(again, res))
             except Exception as e:  # a bounded wait ran out, or the call failed: the device stays usable
                 print(f"rank {rank}: in-kernel exchange failed its check: {e}", file=sys.stderr)
                 ok = False
-            flags = [None] * world
-            dist.all_gather_object(flags, ok)
-            ok = all(flags)
+            ok = all(gather(ok))
         if ok:
             exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
+            checks["vs_nccl_path_bit_equal"] = True
         else:
             group.disable_peer_exchange()
             print(f"rank {rank}: staying on the NCCL exchange", file=sys.stderr)
 
-    # ---- timed region: K steps, device-resident input ----
+    def record_step():
+        """Runs one step for real through the recorder; returns (its call list, its results)."""
+        group.flush()
+        dev.synchronize()
+        recorder.start()
+        out = step(rotating)
+        group.flush()
+        got = [r.numpy() for r in out]
+        del out
+        return recorder.finish(local, keep=xs), got
+
+    # ---- timed region: K steps (repeated until the region lasts long enough), device-resident input ----
     def timed_region():
-        """Warm-up, then K timed steps. Returns None if a step failed or the last step's results are not
-        the gate's (possible only with the in-kernel exchange: a peer wait that ran out)."""
+        """Warm-up, then the timed passes. Returns None if a step failed or the steps' results are not the
+        gate's (possible only with the in-kernel exchange: a peer wait that ran out)."""
         try:
-            for _ in range(args.warmup):
-                step(x)
+            native = group.peer_exchange or world == 1  # the NCCL path's collectives are issued by torch: Python drives it
+            rec, got = record_step() if native else (None, [r.numpy() for r in step(rotating)])
+            if not all(a.tobytes() == b.tobytes() for a, b in zip(got, res)):
+                return None
+
+            def passes(k):
+                if native:
+                    group.advance_peer_seq(rec.run(k, group.peer_seq))
+                else:
+                    for _ in range(k):
+                        step(rotating)
+                    group.flush()
+
+            passes(args.warmup)
+            # Warm-up by time as well as by count; the same run tells how long one pass takes, which
+            # sizes the timed region. Every rank must come to the same counts: rank 0's are used.
+            barrier()
+            t0 = time.perf_counter()
+            probe = 0
+            while True:
+                passes(args.steps)
+                dev.synchronize()
+                probe += args.steps
+                if all(gather(time.perf_counter() - t0 >= args.warmup_seconds)):
+                    break
+            per_pass = (time.perf_counter() - t0) / probe
+            inner = gather(max(1, math.ceil(args.min_seconds / (per_pass * args.steps))))[0]
+            groups = 20 if args.steps * inner >= 20 else 1
+            total = args.steps * inner
+            sizes = [total // groups + (1 if g < total % groups else 0) for g in range(groups)]
             # Everything slow or uneven between ranks (NVML start-up, allocations of events) happens BEFORE the
             # barrier: a rank that starts its first timed reduction late makes every other rank wait for it there.
             sampler = ClockSampler(local)
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-            op_ev = []  # per-op event pairs for the SUM_AXIS launch (first op of each step)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(groups + 1)]
             l0 = launches()
             barrier()
             with sampler as clocks:
                 ev[0].record(stream)
                 t_host = time.perf_counter()
-                for k in range(args.steps):
-                    if world == 1:
-                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        e0.record(stream)
-                        s = x.sum()
-                        e1.record(stream)
-                        op_ev.append((e0, e1))
-                        r = [s, x.mean(), x.max(), x.argmax()]
-                    else:
-                        r = step(x)
-                group.flush()  # combines still deferred behind the last local pass
-                ev[1].record(stream)
-                host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps  # time the host needs to ENQUEUE one step
+                for g, k in enumerate(sizes):  # an event between groups of passes: the median group is reported beside the total
+                    passes(k)
+                    ev[g + 1].record(stream)
+                host_ms = (time.perf_counter() - t_host) * 1e3 / total  # time the host needs to ENQUEUE one step
                 barrier()
             l1 = launches()
-            same = all(a.numpy().tobytes() == b.tobytes() for a, b in zip(r, res))  # after the timed region: the steps computed the gate's values
-            return (ev, op_ev, l0, l1, clocks, host_ms) if same else None
+            # after the timed region: one more step, read back, must still be the gate's values
+            same = all(a.numpy().tobytes() == b.tobytes() for a, b in zip(step(rotating), res))
+            if not same:
+                return None
+            ms_total = ev[0].elapsed_time(ev[-1])
+            per_group = [ev[g].elapsed_time(ev[g + 1]) / sizes[g] for g in range(groups)]
+            return {"ms": ms_total, "passes": total, "inner": inner, "launches": int(l1 - l0), "clocks": clocks, "host_ms": host_ms,
+                    "median_ms": statistics.median(per_group), "calls_per_pass": rec.executes if native else None,
+                    "driver": "recorded call list replayed by pytorches_b200_replay" if native else "Python mirror of the core"}
         except pytorches_b200.abi.PluginError as e:
             print(f"rank {rank}: timed region failed: {e}", file=sys.stderr)
             return None
 
     timed = timed_region()
     if world > 1:
-        flags = [None] * world
-        dist.all_gather_object(flags, timed is not None)
+        flags = gather(timed is not None)
         if not all(flags) and group.peer_exchange:  # every rank goes back to NCCL together and measures again
             print(f"rank {rank}: in-kernel exchange failed during the timed region; measuring with NCCL", file=sys.stderr)
             group.disable_peer_exchange()
+            checks.pop("vs_nccl_path_bit_equal", None)
             exchange = "NCCL all-gather of the partials, combined by plugin ops (the in-kernel exchange failed in this run)"
             try:
                 dev.synchronize()
             except pytorches_b200.abi.PluginError:
                 pass  # the deferred report of the failed wait, if this rank had not seen it yet
             timed = timed_region()
-            dist.all_gather_object(flags, timed is not None)
+            flags = gather(timed is not None)
         if not all(flags):
             raise SystemExit("the timed steps failed or did not reproduce the gate's results")
     elif timed is None:
         raise SystemExit("the timed steps failed or did not reproduce the gate's results")
-    ev, op_ev, l0, l1, clocks, host_ms = timed
-    ms = ev[0].elapsed_time(ev[1])
+    ms = timed["ms"]
     t_ms = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
     rank_ms = [ms]
     if world > 1:
@@ -335,32 +447,35 @@ def main():
         rank_ms = [float(t.item()) for t in all_ms]
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
     ms = float(t_ms.item())
-    bytes_per_step = len(OPS) * 4 * N_ELEMS * world
-    value = bytes_per_step * args.steps / (ms * 1e-3) / 1e9
+    bytes_per_step = len(OPS) * 4 * N_ELEMS  # the whole job: all ranks' shards together are the one tensor
+    value = bytes_per_step * timed["passes"] / (ms * 1e-3) / 1e9
 
     # ---- N > 1: the same four passes on every rank with NO exchange, all ranks at once. The gap between
     # the sharded step and the slowest rank's local passes is what the exchange and the combines cost. ----
     local_ms = None
     if world > 1:
-        k_local = min(args.steps, 20)
+        recorder.start()
+        out = [rotating(0).sum(), rotating(1).mean(), rotating(2).max(), rotating(3).argmax()]
+        del out
+        rec_local = recorder.finish(local, keep=xs)
+        k_local = max(args.steps, 20)
+        rec_local.run(args.warmup)
         barrier()
         la, lb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         la.record(stream)
-        for _ in range(k_local):
-            r = [x.sum(), x.mean(), x.max(), x.argmax()]
+        rec_local.run(k_local)
         lb.record(stream)
         barrier()
-        mine = torch.tensor([la.elapsed_time(lb) / k_local], dtype=torch.float64, device=f"cuda:{local}")
-        every = [torch.zeros_like(mine) for _ in range(world)]
-        dist.all_gather(every, mine)
-        local_ms = [round(float(t.item()), 4) for t in every]
+        local_ms = [round(v, 4) for v in gather(la.elapsed_time(lb) / k_local)]
 
-    # ---- per-op device times (N = 1): every op alone, K launches each, for the breakdown ----
-    per_op = {}
+    # ---- the dominant kernel alone, and every op alone (N = 1): K launches each with an event pair around
+    # every launch, for the roofline and the breakdown ----
+    per_op, sum_ms = {}, None
     if world == 1:
+        x = xs[0]
         for name, fn in (("sum", x.sum), ("mean", x.mean), ("max", x.max), ("argmax", x.argmax)):
             pairs = []
-            for _ in range(min(args.steps, 50)):
+            for _ in range(min(max(args.steps, 20), 50)):
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream)
                 fn()
@@ -369,58 +484,54 @@ def main():
             dev.synchronize()
             torch.cuda.synchronize()
             per_op[name] = statistics.mean(a.elapsed_time(b) for a, b in pairs)
+        sum_ms = per_op["sum"]
 
     # ---- end to end: the same step from pinned host memory through copy_from_host, results read back ----
-    e2e = None
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.e2e_steps):
-        xe = Tensor.from_numpy(host_np, dev)        # host -> device, 1 GiB, inside the timed region
-        out = [r.numpy() for r in step(xe)]         # blocking device -> host reads of the four results
+        xe = Tensor.from_numpy(host_np, dev)                 # host -> device, this rank's shard, inside the timed region
+        out = [r.numpy() for r in step(lambda j: xe)]        # blocking device -> host reads of the four results
         del xe
     barrier()
-    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-    t_e = torch.tensor([e2e_s], dtype=torch.float64, device=f"cuda:{local}")
-    if world > 1:
-        dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-    e2e_s = float(t_e.item())
-    e2e = {"value": round(bytes_per_step / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": 4 * N_ELEMS * world,
+    e2e_s = max(gather((time.perf_counter() - t0) / args.e2e_steps))
+    assert all(a.tobytes() == b.tobytes() for a, b in zip(out, res)), "the end-to-end step's results differ from the gate's"
+    e2e = {"value": round(bytes_per_step / e2e_s / 1e9, 3), "unit": "GB/s", "h2d_bytes_per_step": 4 * N_ELEMS,
            "d2h_bytes_per_step": (4 + 4 + 4 + 8) * world, "ms_per_step": round(e2e_s * 1e3, 3), "steps": args.e2e_steps}
 
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     peak, peak_kind = measured_peak_gbs()
     roofline = None
-    if op_ev:
-        sum_ms = statistics.mean(a.elapsed_time(b) for a, b in op_ev)
+    if sum_ms:
         achieved = 4 * N_ELEMS / (sum_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": "sum_rows_tma_kernel<fused>: one SUM_AXIS over 2^28 f32 (streaming pass with the ordered combine in the same launch)", "achieved": round(achieved, 1),
-                    "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_8TBps": round(achieved / 8000.0, 4),
-                    "algorithmic_bytes_per_launch": 4 * N_ELEMS, "ms_per_launch": round(sum_ms, 5), "traffic": NCU_TRAFFIC_PER_LAUNCH}
+        roofline = {"bound": "hbm", "kernel": "sum_rows_tma_kernel<fused>: one SUM_AXIS over 2^28 f32 (streaming pass with the ordered combine in the same launch)",
+                    "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                    "frac_of_8TBps": round(achieved / 8000.0, 4), "algorithmic_bytes_per_launch": 4 * N_ELEMS, "ms_per_launch": round(sum_ms, 5),
+                    "timing": "mean over launches issued one by one with a CUDA event pair around each, after the timed region",
+                    "traffic": int(NCU_READ_BYTES_PER_ELEMENT * N_ELEMS + NCU_WRITE_BYTES_PER_LAUNCH)}
     cpu = None
     if world == 1:
         gbs, cores, steps, per_step = run_cpu_baseline(args.cpu_seconds)
         cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                "sample": f"full workload, {steps} steps of {per_step * 1e3:.1f} ms on {cores} host threads (C++ restatement of the reference CPU plugin)"}
-    line = {
+    passes = timed["passes"]
+    return {
         "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms / args.steps, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": "config 2: full-tensor f32 sum/mean/max/argmax over 2^28 elements (1 GiB) per GPU", "elements_per_gpu": N_ELEMS,
-                   "ops": list(OPS), "sharding": f"dim 0 over {world} GPU(s); exchange: {exchange}" if world > 1 else "none",
-                   "l2": "input (1 GiB) is larger than L2 (126 MB); no flush needed", "frac_of_measured_peak": round(value / (peak * world), 4),
-                   "frac_of_8TBps": round(value / (8000.0 * world), 4)},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(l1 - l0), "host_enqueue_ms_per_step": round(host_ms, 4), "rank_ms_per_step": [round(v / args.steps, 4) for v in rank_ms],
-        "rank_local_ms_per_step_no_exchange": local_ms, "roofline": roofline, "cpu_baseline": cpu,
-        "ops_ms": {k: round(v, 5) for k, v in per_op.items()}, "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
+        "ms_per_step": round(ms / passes, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(world),
+        "method": {"inner_repeats": timed["inner"], "timed_steps": passes, "timed_region_ms": round(ms, 3),
+                   "ms_per_step_median_of_groups": round(timed["median_ms"], 5), "copies_in_rotation": copies,
+                   "bytes_in_rotation": copies * 4 * n_local, "driven_by": timed["driver"], "calls_per_step": timed["calls_per_pass"],
+                   "exchange": exchange if world > 1 else "none", "warmup_seconds": args.warmup_seconds},
+        "frac_of_measured_peak": round(value / (peak * world), 4), "frac_of_8TBps": round(value / (8000.0 * world), 4),
+        "clocks": timed["clocks"].summary(), "e2e": e2e, "gpu_launches": timed["launches"], "host_enqueue_ms_per_step": round(timed["host_ms"], 5),
+        "rank_ms_per_step": [round(v / passes, 5) for v in rank_ms], "rank_local_ms_per_step_no_exchange": local_ms,
+        "roofline": roofline, "cpu_baseline": cpu, "ops_ms": {k: round(v, 5) for k, v in per_op.items()},
+        "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
+        "results_check": checks,
     }
-    sys.stdout.flush()
-    os.write(real_stdout, (json.dumps(line) + "\n").encode())
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

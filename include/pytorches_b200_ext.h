@@ -27,6 +27,18 @@ extern "C" {
 void *pytorches_b200_stream(uint32_t device);
 
 /*
+ * Tells the plugin that the host has put work of its own on `device`'s stream (the one above).
+ * The plugin lets a full-tensor reduction START while the previous one it enqueued is still in its
+ * last microseconds (the ordered combine of the block sums, the exchange with peer GPUs), when it
+ * enqueued nothing else between the two and their buffers are disjoint; results and their order are
+ * unaffected. It cannot see a kernel the host launches on the stream directly, so after doing that
+ * the host calls this once and the next reduction is launched the ordinary way. Event records,
+ * event waits and copies need no call: they separate the kernels around them by themselves.
+ * Replaces nothing in the reference.
+ */
+void pytorches_b200_stream_touched(uint32_t device);
+
+/*
  * Number of CUDA kernels this library has launched since it was loaded (all devices, all threads).
  * Copies are not counted. Replaces nothing in the reference.
  */
@@ -52,7 +64,9 @@ uint64_t pytorches_b200_kernel_launches(void);
  *   stream  the cudaStream_t to enqueue on (NULL is CUDA's default stream); the call returns
  *           once the kernels are queued, like the vtable's execute
  *
- * The result is bit-identical to SUM_AXIS over a 1-D tensor of the same data. Returns a PtStatus.
+ * The result is bit-identical to SUM_AXIS over a 1-D tensor of the same data. Returns a PtStatus;
+ * after a failure last_error() of the vtable says why. The calling thread's current CUDA device is
+ * the same after the call as before it.
  *
  * The first call on each device looks up the array's address on that device (one
  * cudaGetSymbolAddress); make that first call outside any stream capture. All calls on one GPU share
@@ -85,14 +99,68 @@ int32_t pytorches_b200_sum_noalloc(uint32_t device, const float *x, uint64_t n, 
  * `out`; every rank ends with the same bits, those the vtable ops give when they combine the gathered
  * per-rank results (SUM_AXIS / MAX_AXIS / ARGMAX_COMBINE over a [world, ...] tensor).
  *
+ * pytorches_b200_peer_mean(device, x, n, n_total, seq, out) is the mean of the whole tensor of
+ * n_total elements: the sum as above, divided in the same kernel by n_total as an f32. Same bits as
+ * the reference's mean over the gathered per-rank sums, which is SUM_AXIS then DIV by a scalar tensor
+ * holding the element count (crates/core/src/lib.rs:662-670).
+ *
  * `seq` numbers the reductions of the group: every rank must pass the same value for the same
  * reduction and a different one for the next (a counter). All ranks must call in the same order. If
  * a peer's result does not arrive within wait_ms the kernel gives up, nothing hangs, and the next
  * blocking vtable call on the device returns PT_STATUS_INTERNAL once. All return a PtStatus.
+ *
+ * `x` may be any f32 device pointer of that GPU (4-byte aligned), not only the start of a plugin
+ * buffer: a pointer that is not 16-byte aligned takes the kernels' narrow-load forms, with the same
+ * result. `out` must be aligned to its type (4 bytes, 8 for argmax). Other alignments are refused
+ * with PT_STATUS_INVALID_ARGUMENT.
  */
 int32_t pytorches_b200_peer_export(uint32_t device, void *handle_out);
 int32_t pytorches_b200_peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms);
 int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out);
+int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, uint64_t n, uint64_t n_total, uint64_t seq, float *out);
+
+/*
+ * Replay of a recorded call list. The reference core issues one `execute` per tensor op, each with
+ * an `alloc` for its result before and `free`s as tensors die (crates/core/src/lib.rs:331-370); a
+ * training or benchmark step repeats the same list of calls every time. This entry point takes such
+ * a list once and issues it `repeats` times from native code, call for call through the same alloc,
+ * free and execute the vtable exposes, so that a host written in a slow language does not become the
+ * bottleneck when the ops run for tens of microseconds. It replaces nothing in the reference (whose
+ * core is native code already); the Python host in this repository records its own op sequences
+ * with it.
+ *
+ * A call is one of: PT_B200_CALL_EXECUTE (`op`, `ints` = the OpAttrs, `in`/`out` = the descriptors),
+ * PT_B200_CALL_ALLOC (ints[0] = bytes, ints[1] = slot: the block is kept in that slot),
+ * PT_B200_CALL_FREE (ints[1] = slot), PT_B200_CALL_PEER_REDUCE (`op` = kind 0 sum, 1 max, 2 argmax,
+ * 3 mean; in[0] = this rank's shard as a 1-D tensor, out[0] = the result; ints[0] = first_index,
+ * ints[1] = the whole tensor's element count for a mean; `seq` is first_seq for the first such call
+ * and counts up from there across calls and repeats). An operand names its memory either directly
+ * (`slot` < 0, `data` = device pointer, which must stay valid) or as the block currently in `slot`.
+ * Blocks still in a slot when a pass over the list ends are freed, as when a host drops the results
+ * of a step. Stops at the first call that fails and returns its PtStatus (last_error() says why).
+ */
+enum { PT_B200_CALL_EXECUTE = 0, PT_B200_CALL_ALLOC = 1, PT_B200_CALL_FREE = 2, PT_B200_CALL_PEER_REDUCE = 3 };
+
+typedef struct PtB200Operand {
+    void *data;
+    int32_t slot;
+    uint32_t dtype;
+    uint32_t ndim; /* at most 8 */
+    uint32_t reserved;
+    uint64_t shape[8];
+    uint64_t strides[8];
+} PtB200Operand;
+
+typedef struct PtB200Call {
+    uint32_t kind;
+    uint32_t op;
+    int64_t ints[4];
+    uint32_t n_in, n_out; /* at most 2 each */
+    PtB200Operand in[2];
+    PtB200Operand out[2];
+} PtB200Call;
+
+int32_t pytorches_b200_replay(uint32_t device, const PtB200Call *calls, uint32_t n_calls, uint32_t repeats, uint64_t first_seq);
 
 /*
  * Failure-path self test. The staged reduction kernels wait for their asynchronous copies with a

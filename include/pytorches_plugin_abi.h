@@ -93,6 +93,12 @@ enum {
 
     PT_OP_FILL = 400,        /* no inputs; ints[0] = f32 bit pattern */
     PT_OP_RAND_NORMAL = 401, /* no inputs; ints[0] = seed; counter-based Box-Muller, see below */
+    /* Appended by this plugin, NOT in the reference: uniform values from the same counter hash, so
+     * that benchmark inputs of gigabytes can be generated where they are used. No inputs; ints[0] =
+     * seed, ints[1] = f32 bits of `lo`, ints[2] = f32 bits of `scale`, ints[3] = counter of element 0.
+     * Element i: h = splitmix64(seed ^ (ints[3] + i) * 0x9E3779B97F4A7C15), u = (h >> 40) / 2^24 in
+     * [0,1), out = lo + scale * u (one rounded multiply, then one rounded add). */
+    PT_OP_RAND_UNIFORM = 402,
 
     PT_OP_AXPY = 500, /* optional; out = in0 + alpha*in1, alpha bits in ints[0]; out may alias in0 */
 

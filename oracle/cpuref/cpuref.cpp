@@ -129,7 +129,7 @@ uint32_t supports_op(uint32_t code) {
     switch (code) {
         case OP_NEG: case OP_EXP: case OP_LOG: case OP_RELU: case OP_TANH: case OP_STEP:
         case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV:
-        case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY: case OP_SUM_AXIS: case OP_COPY: case OP_FILL: case OP_RAND_NORMAL:
+        case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY: case OP_SUM_AXIS: case OP_COPY: case OP_FILL: case OP_RAND_NORMAL: case OP_RAND_UNIFORM:
         case OP_MAX_AXIS: case OP_ARGMAX_AXIS: case OP_MAX_ARGMAX_AXIS: case OP_ARGMAX_COMBINE:
         case OP_RELU_GRAD: case OP_ADD_RELU: case OP_SUB_EXP:
             return 1;
@@ -180,7 +180,7 @@ PtStatus run(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint3
     if (n_out != 1) return PT_STATUS_INVALID_ARGUMENT;  // lib.rs:252-254
     uint32_t need;
     switch (op) {  // lib.rs:255-260
-        case OP_FILL: case OP_RAND_NORMAL: need = 0; break;
+        case OP_FILL: case OP_RAND_NORMAL: case OP_RAND_UNIFORM: need = 0; break;
         case OP_NEG: case OP_EXP: case OP_LOG: case OP_RELU: case OP_TANH: case OP_STEP: case OP_COPY:
         case OP_SUM_AXIS: case OP_MAX_AXIS: case OP_ARGMAX_AXIS: need = 1; break;
         case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV: case OP_MATMUL: case OP_MATMUL_T: case OP_AXPY:
@@ -200,6 +200,14 @@ PtStatus run(uint32_t op, const PtOpAttrs &attrs, const PtTensorDesc *ins, uint3
             break;
         }
         case OP_RAND_NORMAL: randn(out, n, (uint64_t)attrs.ints[0]); break;
+        case OP_RAND_UNIFORM: {
+            uint32_t b1 = (uint32_t)attrs.ints[1], b2 = (uint32_t)attrs.ints[2];
+            float lo, scale;
+            std::memcpy(&lo, &b1, 4);
+            std::memcpy(&scale, &b2, 4);
+            rand_uniform(out, n, (uint64_t)attrs.ints[0], lo, scale, (uint64_t)attrs.ints[3]);
+            break;
+        }
         case OP_NEG: case OP_EXP: case OP_LOG: case OP_RELU: case OP_TANH: case OP_STEP: case OP_COPY:
             if (numel(ins[0].shape, ins[0].ndim) != n) return PT_STATUS_INVALID_ARGUMENT;
             unary(op, (const float *)ins[0].data, ins[0].shape, ins[0].strides, ins[0].ndim, out);

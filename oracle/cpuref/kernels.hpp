@@ -25,7 +25,7 @@ enum : uint32_t {
     OP_ADD = 100, OP_SUB = 101, OP_MUL = 102, OP_DIV = 103,
     OP_MATMUL = 200, OP_SUM_AXIS = 201, OP_MATMUL_T = 202, OP_MAX_AXIS = 203, OP_ARGMAX_AXIS = 204,
     OP_MAX_ARGMAX_AXIS = 205, OP_ARGMAX_COMBINE = 206,
-    OP_COPY = 300, OP_FILL = 400, OP_RAND_NORMAL = 401, OP_AXPY = 500,
+    OP_COPY = 300, OP_FILL = 400, OP_RAND_NORMAL = 401, OP_RAND_UNIFORM = 402, OP_AXPY = 500,
     OP_RELU_GRAD = 501, OP_ADD_RELU = 502, OP_SUB_EXP = 503,  // appended fused ops (not in the reference)
 };
 
@@ -291,6 +291,20 @@ inline void randn(float *out, size_t n, uint64_t seed) {  // ew.rs:371-380
     const size_t chunk = n < PAR_MIN ? std::max(n, (size_t)1) : (size_t(1) << 14);
     Pool::get().for_chunks(n, chunk, [&](size_t lo, size_t hi) {
         for (size_t i = lo; i < hi; ++i) out[i] = rand_normal(seed, (uint64_t)i);
+    });
+}
+
+// RAND_UNIFORM (appended op, not in the reference): the same counter hash, u = (h >> 40) / 2^24,
+// out = lo + scale * u with the multiply and the add rounded separately.
+inline void rand_uniform(float *out, size_t n, uint64_t seed, float lo, float scale, uint64_t first) {
+    const size_t chunk = n < PAR_MIN ? std::max(n, (size_t)1) : (size_t(1) << 14);
+    Pool::get().for_chunks(n, chunk, [&](size_t b, size_t e) {
+        for (size_t i = b; i < e; ++i) {
+            const uint64_t h = splitmix64(seed ^ ((first + (uint64_t)i) * 0x9E3779B97F4A7C15ull));
+            const float u = (float)(h >> 40) / 16777216.0f;
+            const float scaled = scale * u;
+            out[i] = lo + scaled;
+        }
     });
 }
 

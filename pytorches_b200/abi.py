@@ -36,6 +36,7 @@ class op:
     MAX_ARGMAX_AXIS, ARGMAX_COMBINE = 205, 206  # appended, for sharded reductions
     COPY = 300
     FILL, RAND_NORMAL = 400, 401
+    RAND_UNIFORM = 402  # appended: lo + scale * u from the RAND_NORMAL counter hash
     AXPY = 500
     RELU_GRAD, ADD_RELU, SUB_EXP = 501, 502, 503  # appended: optional fused ops, each equal to its two-op sequence
 

@@ -180,6 +180,12 @@ class Tensor:
     def randn_on(shape, seed: int, device: Device) -> "Tensor":
         return run_op(device, op.RAND_NORMAL, [seed], [], list(shape))
 
+    @staticmethod
+    def rand_uniform_on(shape, seed: int, lo: float, hi: float, device: Device, first: int = 0) -> "Tensor":
+        """Uniform [lo, hi) from the counter hash (appended op RAND_UNIFORM, not in the reference):
+        element i is lo + (hi - lo) * u(first + i)."""
+        return run_op(device, op.RAND_UNIFORM, [seed, _f32_bits(lo), _f32_bits(hi - lo), first], [], list(shape))
+
     # ---- access ----
     @property
     def device(self) -> Device:

@@ -21,6 +21,10 @@ int sm_count(int device);
 // Stores `msg` as the calling thread's last error (what the vtable's last_error() returns).
 void set_last_error(const char *msg);
 
+// Tells the boundary that something it did not enqueue itself went onto `device`'s stream: the next
+// reduction is then launched the ordinary way (see LaunchChain).
+void note_foreign_enqueue(int device);
+
 // Exact floor division by a runtime constant. For 32-bit operands: Lemire's method,
 // floor(n/d) = hi64(ceil(2^64/d) * n) for every n, d < 2^32 (d > 1). For 64-bit operands the
 // hardware-emulated division is used; that path only runs for tensors of 2^32 or more work items.
@@ -64,6 +68,7 @@ cudaError_t launch_binary(uint32_t op, const float *a, const float *b, float *ou
 cudaError_t launch_axpy(const float *a, const float *b, float *out, float alpha, uint64_t n, cudaStream_t s);
 cudaError_t launch_fill(float *out, uint64_t n, float v, cudaStream_t s);
 cudaError_t launch_randn(float *out, uint64_t n, uint64_t seed, cudaStream_t s);
+cudaError_t launch_rand_uniform(float *out, uint64_t n, uint64_t seed, float lo, float scale, uint64_t first, cudaStream_t s);
 cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const float *b, uint64_t brs, uint64_t bcs,
                           float *c, uint64_t m, uint64_t n, uint64_t k, cudaStream_t s);
 
@@ -87,6 +92,7 @@ struct PeerXchg {
     int rank;
     uint32_t epoch;          // never 0; the same on every rank for the same reduction
     uint32_t wait_ms;        // how long to wait for the peers before giving up
+    float divide_by;         // a sum's combined result is divided by this when it is not 0 (mean = sum / count)
 };
 // Window management (one window per device of this process). `handle` is a 64-byte CUDA IPC handle.
 cudaError_t peer_window_export(int device, void *handle, cudaStream_t s);
@@ -94,13 +100,32 @@ cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const 
 bool peer_window_for(int device, uint64_t seq, PeerXchg *px);
 
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
+
+// What the boundary remembers about the last thing it enqueued on a device's stream, so that a
+// reduction can be allowed to start while the previous one is still finishing. A full-tensor reduction
+// over a long row ends in one combiner CTA (ordered chain over the block sums, the exchange with peer
+// GPUs); its worker CTAs are long done by then. Such a kernel signals early that dependents may
+// launch, and if the NEXT thing enqueued is again such a reduction with buffers disjoint from this
+// one's, it is launched with programmatic stream serialization: its workers stream while this one's
+// combiner finishes. Ordering is kept where it matters: a combiner first waits for the previous
+// kernel to complete, and only then lets the kernel after its own start, so at most two such kernels
+// are ever in flight and they complete in order; any other kind of work is launched normally and
+// starts after everything before it has completed. `tail_open` is false after anything else.
+struct LaunchChain {
+    bool tail_open = false;
+    const char *in_lo = nullptr, *in_hi = nullptr;  // the open reduction's input range
+    const void *out[2] = {nullptr, nullptr};        // and its outputs
+};
+
 // With `px` (only for outer == inner == 1): the result written is the combination over all ranks, in
 // rank order, of every rank's result; MAX_ARGMAX then needs both outputs, ARGMAX is not offered.
+// `chain` (may be null: no overlap) is read to decide how to launch and updated to describe this launch.
 cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v,
-                          int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px = nullptr);
-// Kernels with bounded device-side waits report an expired wait in a host-visible word; this returns
-// and clears it (0 = nothing happened).
-int take_reduce_status();
+                          int64_t *out_i, int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px = nullptr,
+                          LaunchChain *chain = nullptr, float *spare_v = nullptr);
+// Kernels with bounded device-side waits report an expired wait in a host-visible word, one per
+// device; this returns and clears it (0 = nothing happened).
+int take_reduce_status(int device);
 // Per column of [g, m] candidates (value, position), the position of the best one.
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s);
 
@@ -111,4 +136,23 @@ cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_
     do {                                                                            \
         kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);                 \
         ::b200::g_kernel_launches.fetch_add(1, std::memory_order_relaxed);          \
+    } while (0)
+
+// The same, optionally with programmatic stream serialization: the kernel may start once every CTA of
+// the kernel before it in the stream has signalled (griddepcontrol.launch_dependents) or exited,
+// instead of after that kernel has completed. Only for kernels written for it (see LaunchChain).
+#define B200_LAUNCH_OVERLAP(overlap, kernel, grid_, block_, smem_, stream_, ...)                          \
+    do {                                                                                              \
+        cudaLaunchConfig_t cfg_ = {};                                                                 \
+        cfg_.gridDim = dim3(grid_);                                                                   \
+        cfg_.blockDim = dim3(block_);                                                                  \
+        cfg_.dynamicSmemBytes = (smem_);                                                              \
+        cfg_.stream = (stream_);                                                                     \
+        cudaLaunchAttribute attr_[1];                                                                 \
+        attr_[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                             \
+        attr_[0].val.programmaticStreamSerializationAllowed = 1;                                      \
+        cfg_.attrs = attr_;                                                                           \
+        cfg_.numAttrs = (overlap) ? 1 : 0;                                                            \
+        (void)cudaLaunchKernelEx(&cfg_, kernel, __VA_ARGS__);                                         \
+        ::b200::g_kernel_launches.fetch_add(1, std::memory_order_relaxed);                            \
     } while (0)

@@ -604,13 +604,36 @@ __global__ void __launch_bounds__(EW_BLOCK) randn_kernel(float *__restrict__ out
     }
 }
 
+// RAND_UNIFORM (appended op): lo + scale * u with u = (hash >> 40) / 2^24, counters first, first + 1, ...
+__device__ __forceinline__ float rand_uniform(uint64_t seed, uint64_t i, float lo, float scale) {
+    const uint64_t h = splitmix64(seed ^ (i * 0x9E3779B97F4A7C15ull));
+    const float u = __fdiv_rn((float)(h >> 40), 16777216.0f);
+    return __fadd_rn(lo, __fmul_rn(scale, u));
+}
+
+__global__ void __launch_bounds__(EW_BLOCK) rand_uniform_kernel(float *__restrict__ out, uint64_t n, uint64_t seed, float lo, float scale,
+                                                                uint64_t first) {
+    const uint64_t items = (n + 3) >> 2;
+    const uint64_t w = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
+    if (w >= items) return;
+    const uint64_t i = w << 2, c = first + i;
+    if (i + 4 <= n) {
+        st4(out + i, make_float4(rand_uniform(seed, c, lo, scale), rand_uniform(seed, c + 1, lo, scale), rand_uniform(seed, c + 2, lo, scale),
+                                 rand_uniform(seed, c + 3, lo, scale)));
+    } else {
+        for (uint64_t j = i; j < n; ++j) out[j] = rand_uniform(seed, first + j, lo, scale);
+    }
+}
+
 // ---- required MATMUL: correctness only, outside the measured path --------------------------------------
 // 32x32 shared-memory tiles, k in order with one fused multiply-add per step; any operand strides.
 __global__ void __launch_bounds__(TILE *TILE) matmul_kernel(const float *__restrict__ a, uint64_t ars, uint64_t acs,
                                                              const float *__restrict__ b, uint64_t brs, uint64_t bcs,
-                                                             float *__restrict__ c, uint64_t m, uint64_t n, uint64_t k) {
+                                                             float *__restrict__ c, uint64_t m, uint64_t n, uint64_t k, uint32_t tiles_n) {
     __shared__ float sa[TILE][TILE + 1], sb[TILE][TILE + 1];
-    const uint64_t row = (uint64_t)blockIdx.y * TILE + threadIdx.y, col = (uint64_t)blockIdx.x * TILE + threadIdx.x;
+    // Tiles are numbered along one grid axis (row-major), which has room for 2^31 - 1 of them.
+    const uint32_t tile_row = blockIdx.x / tiles_n, tile_col = blockIdx.x - tile_row * tiles_n;
+    const uint64_t row = (uint64_t)tile_row * TILE + threadIdx.y, col = (uint64_t)tile_col * TILE + threadIdx.x;
     float acc = 0.0f;
     for (uint64_t k0 = 0; k0 < k; k0 += TILE) {
         const uint64_t ka = k0 + threadIdx.x, kb = k0 + threadIdx.y;
@@ -649,6 +672,13 @@ template <typename I, int NOPS> RowsPlan<I, NOPS> make_rows_plan(const EwProblem
     for (int o = 0; o < NOPS; ++o) r.istride[o] = (uint32_t)in.stride[o];
     r.items = (I)(rows * cols);
     return r;
+}
+
+// The rows kernels index with 32 bits while both the work-item count (plus one grid's worth of
+// overshoot) and the inner dim's element count fit: with 4 elements per item the inner dim can reach
+// 2^32 elements while the items still number fewer than 2^32.
+bool rows_plan_fits_32bit(uint64_t items, uint64_t inner) {
+    return items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32) && inner < (1ull << 32);
 }
 
 // float4 access needs: inner size a multiple of 4 and, for operands read with inner stride 1, every
@@ -791,7 +821,7 @@ template <class Fn> cudaError_t run_binary_body(const float *a, const float *b, 
         uint64_t rows = p.n / p.dim[p.nd - 1].size;
         const uint64_t items = rows * ((p.dim[p.nd - 1].size + vec - 1) / vec);
         const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
-        if (items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32)) {
+        if (rows_plan_fits_32bit(items, p.dim[p.nd - 1].size)) {
             auto plan = make_rows_plan<uint32_t, 2>(p, vec);
             if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, a, b, out, plan);
             else B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, a, b, out, plan);
@@ -848,7 +878,7 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         const uint64_t rows = p.n / p.dim[p.nd - 1].size;
         const uint64_t items = rows * ((p.dim[p.nd - 1].size + vec - 1) / vec);
         const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
-        if (items + (uint64_t)EW_BLOCK * EW_UNROLL < (1ull << 32)) {
+        if (rows_plan_fits_32bit(items, p.dim[p.nd - 1].size)) {
             auto plan = make_rows_plan<uint32_t, 1>(p, vec);
             if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
             else B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
@@ -921,10 +951,16 @@ cudaError_t launch_randn(float *out, uint64_t n, uint64_t seed, cudaStream_t s) 
     return cudaGetLastError();
 }
 
+cudaError_t launch_rand_uniform(float *out, uint64_t n, uint64_t seed, float lo, float scale, uint64_t first, cudaStream_t s) {
+    B200_LAUNCH(rand_uniform_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed, lo, scale, first);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const float *b, uint64_t brs, uint64_t bcs, float *c,
                           uint64_t m, uint64_t n, uint64_t k, cudaStream_t s) {
-    const dim3 grid((unsigned)((n + TILE - 1) / TILE), (unsigned)((m + TILE - 1) / TILE));
-    B200_LAUNCH(matmul_kernel, grid, dim3(TILE, TILE), 0, s, a, ars, acs, b, brs, bcs, c, m, n, k);
+    const uint64_t tiles_n = (n + TILE - 1) / TILE, tiles_m = (m + TILE - 1) / TILE;
+    if (tiles_n * tiles_m > 0x7fffffffull) return cudaErrorInvalidValue;  // an output of more than 2^41 elements
+    B200_LAUNCH(matmul_kernel, (unsigned)(tiles_n * tiles_m), dim3(TILE, TILE), 0, s, a, ars, acs, b, brs, bcs, c, m, n, k, (uint32_t)tiles_n);
     return cudaGetLastError();
 }
 

@@ -51,6 +51,7 @@ struct DeviceState {
     std::unordered_map<void *, size_t> live;                      // handed-out blocks -> bucket
     size_t cached_bytes = 0;
     cudaError_t deferred = cudaSuccess;  // a fault seen after its call had already returned OK
+    LaunchChain chain;                   // whether the last thing enqueued leaves room for the next reduction to start early
 };
 
 DeviceState g_dev[MAX_DEVICES];
@@ -197,9 +198,10 @@ void free_buf(uint32_t device, void *ptr) {
 
 // A deferred fault is reported by the next call that can (docs/plugin-abi.md:155-156).
 PtStatus finish_blocking(DeviceState &d, const char *what) {
+    d.chain.tail_open = false;
     cudaError_t e = cudaStreamSynchronize(d.stream);
     if (e == cudaSuccess) {
-        const int gave_up = take_reduce_status();
+        const int gave_up = take_reduce_status((int)(&d - g_dev));
         if (gave_up == 2) {
             set_err("b200: %s: a sharded reduction waited in vain for a peer GPU's result (bounded device-side wait); its result is invalid", what);
             return PT_STATUS_INTERNAL;
@@ -220,6 +222,7 @@ PtStatus copy_from_host(uint32_t device, void *dst, const void *src, size_t byte
     try {
         B200_ENTER(device);
         if (bytes == 0) return PT_STATUS_OK;
+        d.chain.tail_open = false;
         cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, d.stream);
         if (e != cudaSuccess) return cuda_fail("copy_from_host", e);
         // The source is only the caller's for the duration of this call. Pageable memory has been
@@ -256,6 +259,7 @@ PtStatus copy_d2d(uint32_t device, void *dst, const void *src, size_t bytes) {
     try {
         B200_ENTER(device);
         if (bytes == 0) return PT_STATUS_OK;
+        d.chain.tail_open = false;
         cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, d.stream);
         return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("copy_device_to_device", e);
     } catch (...) {
@@ -322,7 +326,7 @@ uint32_t supports_op(uint32_t code) {
         case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV:
         case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS:
         case PT_OP_MAX_ARGMAX_AXIS: case PT_OP_ARGMAX_COMBINE:
-        case PT_OP_COPY: case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_AXPY:
+        case PT_OP_COPY: case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_RAND_UNIFORM: case PT_OP_AXPY:
         case PT_OP_RELU_GRAD: case PT_OP_ADD_RELU: case PT_OP_SUB_EXP:
             return 1;
         default:
@@ -391,7 +395,7 @@ const char *op_name(uint32_t op) {
         case PT_OP_MATMUL: return "MATMUL"; case PT_OP_MATMUL_T: return "MATMUL_T"; case PT_OP_SUM_AXIS: return "SUM_AXIS";
         case PT_OP_MAX_AXIS: return "MAX_AXIS"; case PT_OP_ARGMAX_AXIS: return "ARGMAX_AXIS"; case PT_OP_COPY: return "COPY";
         case PT_OP_MAX_ARGMAX_AXIS: return "MAX_ARGMAX_AXIS"; case PT_OP_ARGMAX_COMBINE: return "ARGMAX_COMBINE";
-        case PT_OP_FILL: return "FILL"; case PT_OP_RAND_NORMAL: return "RAND_NORMAL"; case PT_OP_AXPY: return "AXPY";
+        case PT_OP_FILL: return "FILL"; case PT_OP_RAND_NORMAL: return "RAND_NORMAL"; case PT_OP_RAND_UNIFORM: return "RAND_UNIFORM"; case PT_OP_AXPY: return "AXPY";
         case PT_OP_RELU_GRAD: return "RELU_GRAD"; case PT_OP_ADD_RELU: return "ADD_RELU"; case PT_OP_SUB_EXP: return "SUB_EXP";
         default: return "?";
     }
@@ -432,7 +436,7 @@ PtStatus run_sharded_argmax(DeviceState &d, uint32_t device, uint32_t op, const 
             if (st != PT_STATUS_OK) return st;
         }
         e = launch_reduce(REDUCE_MAX_ARGMAX, (const float *)x.data, outer, len, inner, (float *)outs[0].data, (int64_t *)outs[1].data,
-                          attrs.ints[1], scratch, (int)device, d.stream);
+                          attrs.ints[1], scratch, (int)device, d.stream, nullptr, &d.chain);
         if (scratch) free_locked(d, scratch);
     } else {
         if (n_in != 2 || n_out != 1) B200_INVALID("b200: ARGMAX_COMBINE takes 2 inputs and 1 output, got %u and %u", n_in, n_out);
@@ -446,6 +450,7 @@ PtStatus run_sharded_argmax(DeviceState &d, uint32_t device, uint32_t op, const 
             B200_INVALID("b200: ARGMAX_COMBINE: inputs must share a [G, ...] shape and the output drop its first dim");
         if (m == 0) return PT_STATUS_OK;
         if (ins[0].shape[0] == 0) B200_INVALID("b200: ARGMAX_COMBINE of zero candidates has no value");
+        d.chain.tail_open = false;
         e = launch_argmax_combine((const float *)ins[0].data, (const int64_t *)ins[1].data, ins[0].shape[0], m, (int64_t *)outs[0].data, d.stream);
     }
     if (e != cudaSuccess) return cuda_fail(op_name(op), e);
@@ -458,7 +463,7 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
     if (n_out != 1) B200_INVALID("b200: op %u: %u outputs, expected 1", op, n_out);
     uint32_t need;
     switch (op) {
-        case PT_OP_FILL: case PT_OP_RAND_NORMAL: need = 0; break;
+        case PT_OP_FILL: case PT_OP_RAND_NORMAL: case PT_OP_RAND_UNIFORM: need = 0; break;
         case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP: case PT_OP_COPY:
         case PT_OP_SUM_AXIS: case PT_OP_MAX_AXIS: case PT_OP_ARGMAX_AXIS: need = 1; break;
         case PT_OP_ADD: case PT_OP_SUB: case PT_OP_MUL: case PT_OP_DIV: case PT_OP_MATMUL: case PT_OP_MATMUL_T: case PT_OP_AXPY:
@@ -483,12 +488,16 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
     if (!numel(o.shape, o.ndim, n)) B200_INVALID("b200: %s: output element count overflows", op_name(op));
     float *out = (float *)o.data;
     cudaError_t e = cudaSuccess;
+    if (op != PT_OP_SUM_AXIS && op != PT_OP_MAX_AXIS && op != PT_OP_ARGMAX_AXIS) d.chain.tail_open = false;
     switch (op) {
         case PT_OP_FILL:
             if (n) e = launch_fill(out, n, bits_to_f32(attrs.ints[0]), d.stream);
             break;
         case PT_OP_RAND_NORMAL:
             if (n) e = launch_randn(out, n, (uint64_t)attrs.ints[0], d.stream);
+            break;
+        case PT_OP_RAND_UNIFORM:
+            if (n) e = launch_rand_uniform(out, n, (uint64_t)attrs.ints[0], bits_to_f32(attrs.ints[1]), bits_to_f32(attrs.ints[2]), (uint64_t)attrs.ints[3], d.stream);
             break;
         case PT_OP_NEG: case PT_OP_EXP: case PT_OP_LOG: case PT_OP_RELU: case PT_OP_TANH: case PT_OP_STEP: case PT_OP_COPY: {
             uint64_t nx;
@@ -535,6 +544,9 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
                 B200_INVALID("b200: %s: [%llu,%llu] x [%llu,%llu] does not give [%llu,%llu]", op_name(op), (unsigned long long)m, (unsigned long long)k,
                              (unsigned long long)kb, (unsigned long long)nn, (unsigned long long)o.shape[0], (unsigned long long)o.shape[1]);
             if (n == 0) break;
+            if (((m + 31) / 32) * ((nn + 31) / 32) > 0x7fffffffull)
+                B200_INVALID("b200: %s: an output of [%llu,%llu] is more than this kernel's 2^31 - 1 tiles of 32x32", op_name(op),
+                             (unsigned long long)m, (unsigned long long)nn);
             const uint64_t ars = ta ? A.strides[1] : A.strides[0], acs = ta ? A.strides[0] : A.strides[1];
             const uint64_t brs = tb ? B.strides[1] : B.strides[0], bcs = tb ? B.strides[0] : B.strides[1];
             e = launch_matmul((const float *)A.data, ars, acs, (const float *)B.data, brs, bcs, out, m, nn, k, d.stream);
@@ -561,7 +573,7 @@ PtStatus run(DeviceState &d, uint32_t device, uint32_t op, const PtOpAttrs &attr
                 if (st != PT_STATUS_OK) return st;
             }
             e = launch_reduce(kind, (const float *)x.data, outer, len, inner, kind == REDUCE_ARGMAX ? nullptr : (float *)o.data,
-                              kind == REDUCE_ARGMAX ? (int64_t *)o.data : nullptr, 0, scratch, (int)device, d.stream);
+                              kind == REDUCE_ARGMAX ? (int64_t *)o.data : nullptr, 0, scratch, (int)device, d.stream, nullptr, &d.chain);
             if (scratch) free_locked(d, scratch);
             break;
         }
@@ -590,6 +602,7 @@ PtStatus execute(uint32_t device, uint32_t op, const PtOpAttrs *attrs, const PtT
 
 PtStatus peer_export(uint32_t device, void *handle) {
     B200_ENTER(device);
+    d.chain.tail_open = false;
     cudaError_t e = peer_window_export((int)device, handle, d.stream);
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer window export", e);
 }
@@ -603,14 +616,18 @@ PtStatus peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void 
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer window attach (CUDA IPC)", e);
 }
 
-PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out) {
-    if (kind > 2) B200_INVALID("b200: peer reduce: kind %u is not 0 (sum), 1 (max) or 2 (argmax)", kind);
+// kind: 0 sum, 1 max, 2 argmax, 3 mean (the sum divided by `count`, the whole tensor's element count as f32).
+PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out, float count = 0.0f) {
+    if (kind > 3) B200_INVALID("b200: peer reduce: kind %u is not 0 (sum), 1 (max), 2 (argmax) or 3 (mean)", kind);
     if (!out || (!x && n)) B200_INVALID("b200: peer reduce: null pointer");
-    if (kind != 0 && n == 0) B200_INVALID("b200: peer reduce: max/argmax of an empty shard has no value");
+    if ((kind == 1 || kind == 2) && n == 0) B200_INVALID("b200: peer reduce: max/argmax of an empty shard has no value");
+    if (kind == 3 && !(count > 0.0f)) B200_INVALID("b200: peer mean: the whole tensor's element count must be positive");
+    if (((uintptr_t)x & 3) || ((uintptr_t)out & (kind == 2 ? 7 : 3))) B200_INVALID("b200: peer reduce: x must be 4-byte aligned, out aligned to its type");
     B200_ENTER(device);
     PeerXchg px;
     if (!peer_window_for((int)device, seq, &px)) B200_INVALID("b200: peer reduce: no peer windows attached on device %u", device);
-    const ReduceKind rk = kind == 0 ? REDUCE_SUM : kind == 1 ? REDUCE_MAX : REDUCE_MAX_ARGMAX;
+    px.divide_by = kind == 3 ? count : 0.0f;
+    const ReduceKind rk = (kind == 0 || kind == 3) ? REDUCE_SUM : kind == 1 ? REDUCE_MAX : REDUCE_MAX_ARGMAX;
     void *scratch = nullptr, *value = nullptr;
     const size_t sb = reduce_scratch_bytes(rk, 1, n, 1, (int)device);
     PtStatus st = PT_STATUS_OK;
@@ -619,11 +636,102 @@ PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n,
         if (scratch) free_locked(d, scratch);
         return st;
     }
-    cudaError_t e = launch_reduce(rk, x, 1, n, 1, kind == 2 ? (float *)value : (float *)out, kind == 2 ? (int64_t *)out : nullptr, first_index,
-                                  scratch, (int)device, d.stream, &px);
+    cudaError_t e = launch_reduce(rk, x, 1, n, 1, kind == 2 ? nullptr : (float *)out, kind == 2 ? (int64_t *)out : nullptr, first_index,
+                                  scratch, (int)device, d.stream, &px, &d.chain, (float *)value);
     if (scratch) free_locked(d, scratch);
     if (value) free_locked(d, value);
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer reduce", e);
+}
+
+// ---- replay of a recorded call list (extension entry point) --------------------------------------------------
+
+static_assert(sizeof(PtB200Operand) == 152 && sizeof(PtB200Call) == 656, "replay structs are part of the C ABI");
+
+PtStatus replay(uint32_t device, const PtB200Call *calls, uint32_t n_calls, uint32_t repeats, uint64_t first_seq) {
+    if (!calls && n_calls) B200_INVALID("b200: replay: null call list");
+    int64_t max_slot = -1;
+    for (uint32_t i = 0; i < n_calls; ++i) {
+        const PtB200Call &c = calls[i];
+        if (c.kind > PT_B200_CALL_PEER_REDUCE) B200_INVALID("b200: replay: call %u has unknown kind %u", i, c.kind);
+        if (c.n_in > 2 || c.n_out > 2) B200_INVALID("b200: replay: call %u has %u inputs and %u outputs (at most 2 each)", i, c.n_in, c.n_out);
+        if (c.kind == PT_B200_CALL_ALLOC || c.kind == PT_B200_CALL_FREE) {
+            if (c.ints[1] < 0 || c.ints[1] >= (1 << 20)) B200_INVALID("b200: replay: call %u names slot %lld", i, (long long)c.ints[1]);
+            if (c.ints[1] > max_slot) max_slot = c.ints[1];
+        }
+        for (uint32_t k = 0; k < c.n_in + c.n_out; ++k) {
+            const PtB200Operand &a = k < c.n_in ? c.in[k] : c.out[k - c.n_in];
+            if (a.ndim > 8) B200_INVALID("b200: replay: call %u has an operand of %u dims (at most 8)", i, a.ndim);
+            if (a.slot >= (1 << 20)) B200_INVALID("b200: replay: call %u names slot %d", i, a.slot);
+            if (a.slot > max_slot) max_slot = a.slot;
+        }
+    }
+    std::vector<void *> slots((size_t)(max_slot + 1), nullptr);
+    auto resolve = [&](const PtB200Operand &a, PtTensorDesc &t) {
+        t.data = a.slot >= 0 ? slots[(size_t)a.slot] : a.data;
+        t.dtype = a.dtype;
+        t.ndim = a.ndim;
+        t.shape = a.shape;
+        t.strides = a.strides;
+    };
+    // Newest first, so that the allocator's cache hands the blocks out again in the order of the list:
+    // a result buffer is then never the one the call just before it wrote.
+    auto drop_all = [&] {
+        for (size_t i = slots.size(); i-- > 0;)
+            if (slots[i]) {
+                free_buf(device, slots[i]);
+                slots[i] = nullptr;
+            }
+    };
+    uint64_t seq = first_seq;
+    for (uint32_t r = 0; r < repeats; ++r) {
+        for (uint32_t i = 0; i < n_calls; ++i) {
+            const PtB200Call &c = calls[i];
+            PtStatus st = PT_STATUS_OK;
+            switch (c.kind) {
+                case PT_B200_CALL_ALLOC: {
+                    void *&slot = slots[(size_t)c.ints[1]];
+                    if (slot) free_buf(device, slot);
+                    slot = nullptr;
+                    st = alloc_buf(device, (size_t)c.ints[0], &slot);
+                    break;
+                }
+                case PT_B200_CALL_FREE: {
+                    void *&slot = slots[(size_t)c.ints[1]];
+                    if (slot) free_buf(device, slot);
+                    slot = nullptr;
+                    break;
+                }
+                case PT_B200_CALL_EXECUTE: {
+                    PtTensorDesc ins[2], outs[2];
+                    for (uint32_t k = 0; k < c.n_in; ++k) resolve(c.in[k], ins[k]);
+                    for (uint32_t k = 0; k < c.n_out; ++k) resolve(c.out[k], outs[k]);
+                    PtOpAttrs attrs;
+                    std::memcpy(attrs.ints, c.ints, sizeof attrs.ints);
+                    st = execute(device, c.op, &attrs, ins, c.n_in, outs, c.n_out);
+                    break;
+                }
+                default: {  // PT_B200_CALL_PEER_REDUCE
+                    if (c.n_in != 1 || c.n_out != 1) {
+                        drop_all();
+                        B200_INVALID("b200: replay: call %u: a sharded reduction takes 1 input and 1 output", i);
+                    }
+                    PtTensorDesc x, o;
+                    resolve(c.in[0], x);
+                    resolve(c.out[0], o);
+                    uint64_t n;
+                    if (!numel(x.shape, x.ndim, n)) n = 0;
+                    st = peer_reduce(device, c.op, (const float *)x.data, n, c.ints[0], seq++, o.data, (float)c.ints[1]);
+                    break;
+                }
+            }
+            if (st != PT_STATUS_OK) {
+                drop_all();
+                return st;
+            }
+        }
+        drop_all();  // what the list left allocated dies with the step, as when the host drops its results
+    }
+    return PT_STATUS_OK;
 }
 
 const PtPluginVTable VTABLE = {
@@ -635,6 +743,12 @@ const PtPluginVTable VTABLE = {
 }  // namespace
 
 void set_last_error(const char *msg) { set_err("%s", msg); }
+
+void note_foreign_enqueue(int device) {
+    if (device < 0 || device >= MAX_DEVICES) return;
+    std::lock_guard<std::mutex> lock(g_dev[device].mu);
+    g_dev[device].chain.tail_open = false;
+}
 
 int sm_count(int device) {
     if (device < 0) (void)cudaGetDevice(&device);
@@ -686,9 +800,39 @@ B200_EXPORT int32_t pytorches_b200_peer_attach(uint32_t device, uint32_t rank, u
 B200_EXPORT int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq,
                                                void *out) {
     try {
+        if (kind > 2) {
+            b200::set_last_error("b200: peer reduce: kind is not 0 (sum), 1 (max) or 2 (argmax)");
+            return PT_STATUS_INVALID_ARGUMENT;
+        }
         return b200::peer_reduce(device, kind, x, n, first_index, seq, out);
     } catch (...) {
+        b200::set_last_error("b200: peer reduce raised an exception");
         return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, uint64_t n, uint64_t n_total, uint64_t seq, float *out) {
+    try {
+        return b200::peer_reduce(device, 3, x, n, 0, seq, out, (float)n_total);
+    } catch (...) {
+        b200::set_last_error("b200: peer mean raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_replay(uint32_t device, const PtB200Call *calls, uint32_t n_calls, uint32_t repeats, uint64_t first_seq) {
+    try {
+        return b200::replay(device, calls, n_calls, repeats, first_seq);
+    } catch (...) {
+        b200::set_last_error("b200: replay raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT void pytorches_b200_stream_touched(uint32_t device) {
+    try {
+        b200::note_foreign_enqueue((int)device);
+    } catch (...) {
     }
 }
 

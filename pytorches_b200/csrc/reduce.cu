@@ -79,19 +79,22 @@ __global__ void __launch_bounds__(32 * SUM_WARPS) sum_rows_kernel(const float *_
 // ---- pass 1 for long rows: TMA-staged -------------------------------------------------------------------
 // The order constraint fixes the parallelism at one warp per 65536 elements, too few warps to keep
 // HBM busy with register loads. So the warp lets the TMA engine do the loading: lane 0 keeps
-// TMA_STAGES bulk copies of TMA_CHUNK floats (16 KiB each, 64 KiB per warp) in flight into a
+// STAGES bulk copies of CHUNK floats (16 KiB each in the usual shapes) in flight into a
 // shared-memory ring, each completing on an mbarrier; the warp then reads a landed chunk at stride 32
 // (lane j takes words j, j+32, ...: conflict-free, and exactly "element i goes to slot i mod 32") and
-// adds in order. One warp per CTA, three CTAs per SM by shared memory: 192 KiB in flight per SM.
+// adds in order. One warp per CTA; shared memory decides how many CTAs an SM holds.
 // Bulk copies need 16-byte aligned sources; the host picks this kernel only when every block start is.
 //
 // Every wait is bounded. If a barrier does not complete within the limit the warp gives its other
 // copies in flight the same bounded chance to land, records WAIT_EXPIRED in *status (pinned host
 // memory the next blocking call inspects) and returns without a result.
-constexpr int TMA_STAGES = 4;
-constexpr uint32_t TMA_CHUNK = 4096;  // floats per bulk copy
-constexpr uint32_t TMA_CHUNK_BYTES = TMA_CHUNK * 4;
-constexpr size_t TMA_SMEM = (size_t)TMA_STAGES * TMA_CHUNK_BYTES;
+//
+// The ring's shape is a template parameter, picked from the grid (see pick_ring): a long row has
+// thousands of blocks, CTAs come and go in many waves and a deep ring (4 x 16 KiB, three CTAs per SM)
+// keeps HBM busy; a row of a few hundred blocks (a 128 MiB shard has 512) fits the GPU all at once
+// if the ring is shallow (2 x 16 KiB, six CTAs per SM), and then nothing waits for a second wave.
+constexpr uint32_t TMA_MIN_CHUNK = 4096;  // floats; rows shorter than 8 of these take the register-load kernel
+constexpr size_t ring_bytes(int stages, uint32_t chunk) { return (size_t)stages * chunk * 4; }
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait calls before giving up (each may block briefly)
 constexpr int STATUS_WAIT_EXPIRED = 1;
 
@@ -124,6 +127,13 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                  "l"(src), "r"(bytes), "r"(smem_addr(bar))
                  : "memory");
 }
+
+// Programmatic dependent launch. launch_dependents: "as far as this CTA is concerned, the next kernel
+// in the stream may start"; it starts once every CTA of this grid has said so or exited.
+// wait_for_prior_grid: blocks until the kernel before this one in the stream has completed and its
+// writes are visible (returns at once if this kernel was launched the ordinary way).
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // FUSED (one row only): the ordered chain over the block sums runs INSIDE this launch. CTA 0 is the
 // combiner; CTAs 1..blocks are the workers. A worker publishes its block sum as ONE 64-bit word,
@@ -212,7 +222,8 @@ __device__ __forceinline__ bool peer_allgather(const PeerXchg &px, float v, int6
 
 // Exchanges this GPU's result with the peers and combines all of them in rank order, exactly as the
 // same plugin op would combine a [world] tensor of the per-rank results: SUM adds them one by one to
-// 0.0 and adds that to 0.0 (the row path for rows shorter than 32, sum_short_rows_kernel); MAX and
+// 0.0 and adds that to 0.0 (the row path for rows shorter than 32, sum_short_rows_kernel), and then
+// divides by px.divide_by if that is set (a mean); MAX and
 // MAX_ARGMAX keep the best (value, position): NaN wins, then the larger value, then the lower position.
 // Whole warp, same (v, pos) in every lane; lane 0 writes. Returns without writing if the wait expired.
 __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float v, int64_t pos, float *out_v, int64_t *out_i, int *status) {
@@ -223,7 +234,11 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
     if (kind == REDUCE_SUM) {
         float s = 0.0f;
         for (int r = 0; r < px.world; ++r) s = __fadd_rn(s, __shfl_sync(0xffffffffu, rv, r));
-        if (lane == 0) out_v[0] = __fadd_rn(0.0f, s);
+        s = __fadd_rn(0.0f, s);
+        // A mean is the reference's sum followed by a DIV by the element count as an f32 scalar
+        // (crates/core/src/lib.rs:662-670): one IEEE division, the same bits as FILL + DIV.
+        if (px.divide_by != 0.0f) s = __fdiv_rn(s, px.divide_by);
+        if (lane == 0) out_v[0] = s;
         return;
     }
     float bv = lane < px.world ? rv : __int_as_float(0xff800000);
@@ -253,6 +268,11 @@ constexpr int COMBINER_WORDS = 8;
 __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
                                  const PeerXchg &px) {
     const int lane = threadIdx.x;
+    // The kernel before this one (if this one was allowed to start early) completes first; only then
+    // may the kernel after this one start. So at most two of these kernels are in flight, they finish
+    // in stream order, and mailbox regions and peer-window generations, used in turn, never collide.
+    wait_for_prior_grid();
+    launch_dependents();
     float s = 0.0f;
     for (uint64_t base = 0; base < blocks; base += 32 * COMBINER_WORDS) {
         float v[COMBINER_WORDS];
@@ -298,18 +318,20 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
     if (lane == 0) out[0] = s;
 }
 
-template <bool FUSED>
+template <bool FUSED, int STAGES, uint32_t CHUNK>
 __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
                                                           float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch,
                                                           const __grid_constant__ PeerXchg px) {
+    constexpr uint32_t CHUNK_BYTES = CHUNK * 4;
     extern __shared__ __align__(128) unsigned char tma_smem[];
-    __shared__ uint64_t bars[TMA_STAGES];
+    __shared__ uint64_t bars[STAGES];
     float *ring = reinterpret_cast<float *>(tma_smem);
     if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status, px);
+    if (FUSED) launch_dependents();  // a worker needs nothing from the kernel before and holds nothing the next one wants
     const uint64_t t = FUSED ? blockIdx.x - 1 : blockIdx.x;
     const int lane = threadIdx.x;
     if (lane == 0) {
-        for (int s = 0; s < TMA_STAGES; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -317,28 +339,28 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
     const uint64_t lo = b * SUM_BLOCK;
     const uint32_t m = (uint32_t)(len - lo < SUM_BLOCK ? len - lo : SUM_BLOCK);
     const float *p = x + row * len + lo;
-    const uint32_t chunks = m / TMA_CHUNK;
+    const uint32_t chunks = m / CHUNK;
     if (lane == 0) {
-        for (uint32_t c = 0; c < TMA_STAGES && c < chunks; ++c) {
-            mbar_expect_tx(&bars[c], TMA_CHUNK_BYTES);
-            bulk_load(ring + (size_t)c * TMA_CHUNK, p + (size_t)c * TMA_CHUNK, TMA_CHUNK_BYTES, &bars[c]);
+        for (uint32_t c = 0; c < STAGES && c < chunks; ++c) {
+            mbar_expect_tx(&bars[c], CHUNK_BYTES);
+            bulk_load(ring + (size_t)c * CHUNK, p + (size_t)c * CHUNK, CHUNK_BYTES, &bars[c]);
         }
     }
     float s = 0.0f;
     for (uint32_t c = 0; c < chunks; ++c) {
-        const int st = c % TMA_STAGES;
-        if (!mbar_wait_bounded(&bars[st], (c / TMA_STAGES) & 1)) {
+        const int st = c % STAGES;
+        if (!mbar_wait_bounded(&bars[st], (c / STAGES) & 1)) {
             // Give the copies still in flight (chunks c+1 .. c+STAGES-1) their bounded chance, then stop.
-            for (uint32_t d = c + 1; d < chunks && d < c + TMA_STAGES; ++d) (void)mbar_wait_bounded(&bars[d % TMA_STAGES], (d / TMA_STAGES) & 1);
+            for (uint32_t d = c + 1; d < chunks && d < c + STAGES; ++d) (void)mbar_wait_bounded(&bars[d % STAGES], (d / STAGES) & 1);
             if (lane == 0) {
                 *(volatile int *)status = STATUS_WAIT_EXPIRED;
                 __threadfence_system();
             }
             return;
         }
-        const float *buf = ring + (size_t)st * TMA_CHUNK;
+        const float *buf = ring + (size_t)st * CHUNK;
 #pragma unroll 2
-        for (uint32_t k = 0; k < TMA_CHUNK / 32; k += 32) {
+        for (uint32_t k = 0; k < CHUNK / 32; k += 32) {
             float v[32];
 #pragma unroll
             for (int u = 0; u < 32; ++u) v[u] = buf[lane + 32 * (k + u)];
@@ -346,14 +368,14 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
             for (int u = 0; u < 32; ++u) s = __fadd_rn(s, v[u]);
         }
         __syncwarp();  // every lane is done reading this stage before it is refilled
-        if (lane == 0 && c + TMA_STAGES < chunks) {
-            mbar_expect_tx(&bars[st], TMA_CHUNK_BYTES);
-            bulk_load(ring + (size_t)st * TMA_CHUNK, p + (size_t)(c + TMA_STAGES) * TMA_CHUNK, TMA_CHUNK_BYTES, &bars[st]);
+        if (lane == 0 && c + STAGES < chunks) {
+            mbar_expect_tx(&bars[st], CHUNK_BYTES);
+            bulk_load(ring + (size_t)st * CHUNK, p + (size_t)(c + STAGES) * CHUNK, CHUNK_BYTES, &bars[st]);
         }
     }
-    // What is left of the block (fewer than TMA_CHUNK elements) continues the same slots with loads.
+    // What is left of the block (fewer than CHUNK elements) continues the same slots with loads.
     const uint32_t m32 = m & ~31u;
-    for (uint32_t k = chunks * TMA_CHUNK + lane; k < m32; k += 32) s = __fadd_rn(s, ldf(p + k));
+    for (uint32_t k = chunks * CHUNK + lane; k < m32; k += 32) s = __fadd_rn(s, ldf(p + k));
     s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 8));
     s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 16));
     s = __fadd_rn(s, __shfl_down_sync(0xffffffffu, s, 4));
@@ -567,6 +589,8 @@ __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, 
     float bv = __int_as_float(0xff800000);
     uint64_t bs = ~0ull;
     bool failed = false;
+    wait_for_prior_grid();  // same ordering rule as the sum's combiner
+    launch_dependents();
     for (uint64_t base = 0; base < segs; base += (uint64_t)MAX_CTA * WORDS) {
         float v[WORDS];
         uint32_t missing = 0;
@@ -656,6 +680,7 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
     constexpr int PER_CTA = MAX_CTA / TPT;
     if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
         return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px);
+    if (TPT == MAX_CTA && fused.mailbox != nullptr) launch_dependents();
     const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
     const uint64_t t = cta * PER_CTA + threadIdx.x / TPT;
     const int lane = threadIdx.x % TPT;
@@ -841,34 +866,39 @@ MaxPlan plan_max(uint64_t outer, uint64_t len, int /*sms*/) {
 
 }  // namespace
 
-// One word of pinned, device-visible host memory in which kernels report a bounded wait that ran out
-// (0 = nothing to report). Written by the device, read by the host at the next blocking call.
-int *reduce_status_word() {
-    static int *word = [] {
+// One word per device of pinned, device-visible host memory in which that device's kernels report a
+// bounded wait that ran out (0 = nothing to report). Written by the device, taken (read and cleared in
+// one atomic exchange) by the host at the next blocking call on that device, so a report is delivered
+// exactly once and to the device it belongs to, whichever threads drive the devices.
+int *reduce_status_word(int device) {
+    static int *words = [] {
         int *p = nullptr;
-        if (cudaHostAlloc((void **)&p, sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+        if (cudaHostAlloc((void **)&p, 64 * sizeof(int), cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
             (void)cudaGetLastError();
             return (int *)nullptr;
         }
-        *p = 0;
+        for (int i = 0; i < 64; ++i) p[i] = 0;
         return p;
     }();
-    return word;
+    return words && device >= 0 && device < 64 ? words + device : nullptr;
 }
 
-int take_reduce_status() {
-    int *w = reduce_status_word();
-    if (!w) return 0;
-    const int v = *(volatile int *)w;
-    if (v) *(volatile int *)w = 0;
-    return v;
+int take_reduce_status(int device) {
+    int *w = reduce_status_word(device);
+    return w ? __atomic_exchange_n(w, 0, __ATOMIC_ACQ_REL) : 0;
 }
 
 namespace {
-// The fused sum's mailbox: MAILBOX_SLOTS 64-bit words per device, allocated and zeroed on first use,
-// kept for the life of the process. Each launch gets the next epoch (never 0); when the 32-bit epoch
-// wraps the words are zeroed again, on the stream, so no stale word can match.
-constexpr uint64_t MAILBOX_SLOTS = 1ull << 20;  // one per 65536 elements: rows of up to 2^36 elements
+// The in-launch combiners' mailbox: MAILBOX_REGIONS regions per device, each MAILBOX_SLOTS 64-bit
+// value words followed by as many 64-bit position words (the max/argmax combiner reads a segment's
+// position there), allocated and zeroed on first use and kept for the life of the process. Each
+// launch gets the next epoch (never 0) and the region epoch mod MAILBOX_REGIONS: two launches may be
+// in flight at once (see LaunchChain), never more, so a region is not written again before its last
+// reader is done. When the 32-bit epoch wraps the words are zeroed again, on the stream, so no stale
+// word can match.
+constexpr uint64_t MAILBOX_SLOTS = 1ull << 18;  // a sum's row of up to 2^34 elements, a max's of up to 2^32
+constexpr int MAILBOX_REGIONS = 4;
+constexpr size_t MAILBOX_BYTES = (size_t)MAILBOX_REGIONS * MAILBOX_SLOTS * 2 * 8;
 // PYTORCHES_B200_FUSED_COMBINE=0 in the environment turns the in-launch combines off (two launches
 // per reduction instead of one); a diagnostic switch, read once.
 unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
@@ -884,7 +914,7 @@ unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
     std::lock_guard<std::mutex> lock(mu);
     if (!box[device]) {
         void *p = nullptr;
-        if (cudaMalloc(&p, MAILBOX_SLOTS * 8) != cudaSuccess || cudaMemsetAsync(p, 0, MAILBOX_SLOTS * 8, s) != cudaSuccess) {
+        if (cudaMalloc(&p, MAILBOX_BYTES) != cudaSuccess || cudaMemsetAsync(p, 0, MAILBOX_BYTES, s) != cudaSuccess) {
             (void)cudaGetLastError();
             if (p) (void)cudaFree(p);
             return nullptr;
@@ -892,14 +922,37 @@ unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
         box[device] = (unsigned long long *)p;
     }
     if (++next[device] == 0) {
-        if (cudaMemsetAsync(box[device], 0, MAILBOX_SLOTS * 8, s) != cudaSuccess) {
+        if (cudaMemsetAsync(box[device], 0, MAILBOX_BYTES, s) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
         next[device] = 1;
     }
     *epoch = next[device];
-    return box[device];
+    return box[device] + (size_t)(next[device] % MAILBOX_REGIONS) * MAILBOX_SLOTS * 2;
+}
+
+// PYTORCHES_B200_OVERLAP=0 turns the early start of back-to-back reductions off (diagnostic, read once).
+bool overlap_enabled() {
+    static const bool enabled = [] {
+        const char *e = getenv("PYTORCHES_B200_OVERLAP");
+        return !(e && e[0] == '0');
+    }();
+    return enabled;
+}
+
+// The staged row sum's ring shapes (stages, floats per copy). pick_ring chooses by the number of
+// worker CTAs: see the comment at TMA_MIN_CHUNK. PYTORCHES_B200_SUM_RING=<index> forces one (diagnostic).
+struct RingShape { int stages; uint32_t chunk; };
+constexpr RingShape RINGS[] = {{4, 4096}, {2, 4096}, {3, 4096}, {4, 2048}, {2, 8192}};
+constexpr int N_RINGS = sizeof(RINGS) / sizeof(RINGS[0]);
+int pick_ring(uint64_t tasks, int sms) {
+    static const int forced = [] {
+        const char *e = getenv("PYTORCHES_B200_SUM_RING");
+        return e && e[0] >= '0' && e[0] < '0' + N_RINGS ? e[0] - '0' : -1;
+    }();
+    if (forced >= 0) return forced;
+    return tasks <= (uint64_t)sms * 12 ? 1 : 0;
 }
 
 // Opts the staged kernels into their 64 KiB of dynamic shared memory, once per device.
@@ -910,8 +963,16 @@ bool staged_kernels_ready(int device) {
     std::lock_guard<std::mutex> lock(mu);
     if (!done[device]) {
         done[device] = true;
-        ok[device] = cudaFuncSetAttribute(sum_rows_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
-                     cudaFuncSetAttribute(sum_rows_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TMA_SMEM) == cudaSuccess &&
+        bool good = true;
+#define B200_RING_ATTR(I)                                                                                                              \
+    good = good &&                                                                                                                     \
+           cudaFuncSetAttribute(sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                (int)ring_bytes(RINGS[I].stages, RINGS[I].chunk)) == cudaSuccess &&                                    \
+           cudaFuncSetAttribute(sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                (int)ring_bytes(RINGS[I].stages, RINGS[I].chunk)) == cudaSuccess;
+        B200_RING_ATTR(0) B200_RING_ATTR(1) B200_RING_ATTR(2) B200_RING_ATTR(3) B200_RING_ATTR(4)
+#undef B200_RING_ATTR
+        ok[device] = good &&
                      cudaFuncSetAttribute(sum_cols_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(128)) == cudaSuccess &&
                      cudaFuncSetAttribute(sum_cols_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(256)) == cudaSuccess;
         if (!ok[device]) (void)cudaGetLastError();
@@ -1046,13 +1107,44 @@ size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint6
 }
 
 namespace {
+bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+// May a reduction of [x, x + n) into out_v / out_i start while the reduction `c` describes is still
+// finishing? Only if neither touches what the other writes.
+bool may_overlap(const LaunchChain *c, const float *x, uint64_t n, const void *out_v, const void *out_i) {
+    if (!c || !c->tail_open || !overlap_enabled()) return false;
+    const char *lo = (const char *)x, *hi = lo + n * sizeof(float);
+    for (const void *o : c->out) {
+        if (!o) continue;
+        if ((const char *)o >= lo && (const char *)o < hi) return false;  // it writes into our input
+        if (o == out_v || o == out_i) return false;                       // both write the same word: order would matter
+    }
+    for (const void *o : {out_v, out_i})
+        if (o && (const char *)o >= c->in_lo && (const char *)o < c->in_hi) return false;  // we write into its input
+    return true;
+}
+
+void chain_opened(LaunchChain *c, const float *x, uint64_t n, const void *out_v, const void *out_i) {
+    if (!c) return;
+    c->tail_open = true;
+    c->in_lo = (const char *)x;
+    c->in_hi = c->in_lo + n * sizeof(float);
+    c->out[0] = out_v;
+    c->out[1] = out_i;
+}
+
 // The local reduction. With `px`, a launch that ends in a combiner CTA also does the cross-GPU step
 // there and sets *peer_done; every other path leaves it to the caller.
 cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
-                                int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px, bool *peer_done) {
+                                int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px, bool *peer_done,
+                                const LaunchChain *prev, LaunchChain *next, float *spare_v) {
     const PeerXchg no_peers{};
     const uint64_t total = outer * inner;
     if (total == 0) return cudaSuccess;
+    // Bulk copies and 128-bit loads need a 16-byte aligned base. Buffers of the plugin's allocator always
+    // are; a pointer a host passes to an extension entry point need not be, and then the register-load
+    // forms of the same kernels run (same order of operations, same bits).
+    const bool base16 = aligned16(x);
     if (kind == REDUCE_SUM) {
         float *o = out_v;
         if (len == 0) return launch_fill(o, total, 0.0f, s);  // reduce.rs:106-109
@@ -1064,19 +1156,31 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
             const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK, tasks = outer * blocks;
             float *dst = blocks == 1 ? o : (float *)scratch;
             // Long rows whose block starts are 16-byte aligned take the TMA-staged kernel.
-            int *status = (len >= 8 * TMA_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word() : nullptr;
+            int *status = (base16 && len >= 8 * TMA_MIN_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word(device) : nullptr;
             if (status && staged_kernels_ready(device)) {
                 // A single long row: chain the block sums inside the same launch (see ordered_combiner).
                 uint32_t epoch = 0;
                 unsigned long long *mailbox = (outer == 1 && blocks >= 64 && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
+                const int ring = pick_ring(tasks, sm_count(device));
+                const bool early = mailbox && may_overlap(prev, x, len, o, nullptr);
+#define B200_RING_CASE(I)                                                                                                                   \
+    if (ring == I) {                                                                                                                        \
+        if (mailbox)                                                                                                                        \
+            B200_LAUNCH_OVERLAP(early, (sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + 1, 32,               \
+                                ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, o, status, mailbox, epoch,           \
+                                px ? *px : no_peers);                                                                                       \
+        else                                                                                                                                \
+            B200_LAUNCH((sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks, 32,                                 \
+                        ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, dst, status, (unsigned long long *)nullptr,  \
+                        0u, no_peers);                                                                                                      \
+    }
+                B200_RING_CASE(0) B200_RING_CASE(1) B200_RING_CASE(2) B200_RING_CASE(3) B200_RING_CASE(4)
+#undef B200_RING_CASE
                 if (mailbox) {
-                    B200_LAUNCH(sum_rows_tma_kernel<true>, (unsigned)tasks + 1, 32, TMA_SMEM, s, x, tasks, len, blocks, o, status, mailbox, epoch,
-                                px ? *px : no_peers);
                     *peer_done = px != nullptr;
+                    chain_opened(next, x, len, o, nullptr);
                     return cudaGetLastError();
                 }
-                B200_LAUNCH(sum_rows_tma_kernel<false>, (unsigned)tasks, 32, TMA_SMEM, s, x, tasks, len, blocks, dst, status,
-                            (unsigned long long *)nullptr, 0u, no_peers);
             } else {
                 B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
             }
@@ -1087,10 +1191,10 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         // columns already give the plain thread-per-column kernel enough loads in flight. The tile
         // coordinates are 32-bit and the row pitch must be a multiple of 16 bytes.
         const uint64_t groups_per_outer = (inner + 31) / 32;
-        if (inner % 4 == 0 && inner >= 32 && len >= 128 && total < (1ull << 19) && outer * len < 0x7fffffffull &&
+        if (base16 && inner % 4 == 0 && inner >= 32 && len >= 128 && total < (1ull << 19) && outer * len < 0x7fffffffull &&
             outer * groups_per_outer <= 0x7fffffffull && staged_kernels_ready(device)) {
             CUtensorMap map;
-            int *status = reduce_status_word();
+            int *status = reduce_status_word(device);
             const unsigned ctas = (unsigned)(outer * groups_per_outer);
             const bool tall = ctas < 2u * (unsigned)sm_count(device) && len >= 1024;
             if (status && make_cols_tensor_map(&map, x, outer * len, inner, tall ? 256 : 128)) {
@@ -1110,8 +1214,27 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         B200_LAUNCH(max_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi, idx_offset);
         return cudaGetLastError();
     }
-    const MaxPlan m = plan_max(outer, len, sm_count(device));
+    MaxPlan m = plan_max(outer, len, sm_count(device));
+    if (!base16) m.vec = 1;
     const uint64_t tasks = outer * m.segs;
+    unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
+    // A single long row: pick the best segment inside the same launch (see max_combiner). The segment
+    // positions then live in the mailbox region, not in scratch: scratch goes back to the allocator
+    // when this call returns and the next launch may start before this one's combiner has read them.
+    MaxFused fused{};
+    bool early = false;
+    if (outer == 1 && m.tpt == MAX_CTA && m.segs >= 64 && m.segs <= MAILBOX_SLOTS) {
+        int *status = reduce_status_word(device);
+        uint32_t epoch = 0;
+        unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
+        if (mailbox) {
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers};
+            grid += 1;
+            *peer_done = px != nullptr;
+            early = may_overlap(prev, x, len, ov, oi);
+        }
+    }
+    if (!fused.mailbox && !ov && spare_v) ov = spare_v;  // the maximum must rest somewhere until the exchange launch reads it
     float *pv = ov;
     int64_t *pi = oi;
     int64_t off1 = idx_offset;
@@ -1120,42 +1243,44 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         pi = arg ? (int64_t *)((char *)scratch + ((tasks * 4 + 15) & ~15ull)) : nullptr;
         off1 = 0;
     }
-    unsigned grid = (unsigned)((tasks + (MAX_CTA / m.tpt) - 1) / (MAX_CTA / m.tpt));
-    // A single long row: pick the best segment inside the same launch (see max_combiner).
-    MaxFused fused{};
-    if (outer == 1 && m.tpt == MAX_CTA && m.segs >= 64 && m.segs <= MAILBOX_SLOTS) {
-        int *status = reduce_status_word();
-        uint32_t epoch = 0;
-        unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
-        if (mailbox) {
-            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers};
-            grid += 1;
-            *peer_done = px != nullptr;
-        }
-    }
-#define B200_MAX_CASE(TPT, VEC)                                                                                                              \
-    if (m.tpt == TPT && m.vec == VEC) {                                                                                                      \
-        if (arg) B200_LAUNCH((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);  \
-        else B200_LAUNCH((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);     \
+    if (fused.mailbox) pi = arg ? (int64_t *)(fused.mailbox + MAILBOX_SLOTS) : nullptr;
+#define B200_MAX_CASE(TPT, VEC)                                                                                                                        \
+    if (m.tpt == TPT && m.vec == VEC) {                                                                                                                \
+        if (arg) B200_LAUNCH_OVERLAP(early, (max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);  \
+        else B200_LAUNCH_OVERLAP(early, (max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);     \
     }
     B200_MAX_CASE(32, 1)
     B200_MAX_CASE(32, 4)
     B200_MAX_CASE(256, 1)
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
+    if (fused.mailbox) chain_opened(next, x, len, ov, oi);
     if (m.segs > 1 && !fused.mailbox) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
     return cudaGetLastError();
 }
 }  // namespace
 
 cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint64_t len, uint64_t inner, float *out_v, int64_t *out_i,
-                          int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px) {
-    if (px && (px->world <= 0 || outer != 1 || inner != 1 || kind == REDUCE_ARGMAX || !out_v || (kind == REDUCE_MAX_ARGMAX && !out_i)))
+                          int64_t idx_offset, void *scratch, int device, cudaStream_t s, const PeerXchg *px, LaunchChain *chain, float *spare_v) {
+    // Across GPUs the maximum travels with its position. A caller that wants the position only passes
+    // out_v = null and `spare_v`, a float of its own that nothing else uses: it is written only when
+    // the local result has to rest in memory between two launches (an input too short for a combiner CTA).
+    const bool position_only = px && kind == REDUCE_MAX_ARGMAX && !out_v && spare_v;
+    if (px && (px->world <= 0 || outer != 1 || inner != 1 || kind == REDUCE_ARGMAX || (!out_v && !position_only) ||
+               (kind == REDUCE_MAX_ARGMAX && !out_i)))
         return cudaErrorInvalidValue;
     bool peer_done = false;
-    cudaError_t e = launch_reduce_local(kind, x, outer, len, inner, out_v, out_i, idx_offset, scratch, device, s, px, &peer_done);
+    LaunchChain before;
+    if (chain) {
+        before = *chain;
+        chain->tail_open = false;  // unless this launch turns out to be one that leaves its tail open
+    }
+    cudaError_t e = launch_reduce_local(kind, x, outer, len, inner, out_v, out_i, idx_offset, scratch, device, s, px, &peer_done,
+                                        chain ? &before : nullptr, chain, position_only ? spare_v : nullptr);
     if (e != cudaSuccess || !px || peer_done) return e;
-    int *status = reduce_status_word();
+    if (chain) chain->tail_open = false;
+    if (position_only) out_v = spare_v;  // where the local pass left this GPU's maximum
+    int *status = reduce_status_word(device);
     if (!status) return cudaErrorMemoryAllocation;
     B200_LAUNCH(peer_exchange_kernel, 1, 32, 0, s, *px, (int)kind, out_v, kind == REDUCE_MAX_ARGMAX ? out_i : (int64_t *)nullptr, status);
     return cudaGetLastError();
@@ -1218,6 +1343,17 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noa
             set_last_error("b200: sum_noalloc: null input or output");
             return 3;
         }
+        // The caller's current device is put back before returning: a host framework that set it for its
+        // own work must not find it changed by a library call.
+        struct RestoreDevice {
+            int prev = -1;
+            ~RestoreDevice() { if (prev >= 0) (void)cudaSetDevice(prev); }
+        } restore;
+        if (cudaGetDevice(&restore.prev) != cudaSuccess) {
+            (void)cudaGetLastError();
+            restore.prev = -1;
+        }
+        if (restore.prev == (int)device) restore.prev = -1;  // nothing to put back
         cudaError_t e = cudaSetDevice((int)device);
         float *partials = nullptr;
         if (e == cudaSuccess) {
@@ -1238,6 +1374,7 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noa
             return 4;  // PT_STATUS_INTERNAL
         }
         cudaStream_t s = (cudaStream_t)stream;
+        note_foreign_enqueue((int)device);  // `stream` may be the plugin's own: what follows there starts the ordinary way
         if (n == 0) {
             e = launch_fill(out, 1, 0.0f, s);  // the sum of nothing is 0.0 (reduce.rs:106-109)
         } else if (n < 32) {
@@ -1260,6 +1397,7 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_sum_noa
         }
         return 0;
     } catch (...) {
+        set_last_error("b200: sum_noalloc raised an exception");
         return 4;
     }
 }
@@ -1298,12 +1436,13 @@ extern "C" __attribute__((visibility("default"))) int32_t pytorches_b200_selftes
             set_last_error("b200: selftest_expired_wait: no such device");
             return 3;
         }
-        int *status = reduce_status_word();
+        int *status = reduce_status_word((int)device);
         if (!status || cudaSetDevice((int)device) != cudaSuccess) {
             (void)cudaGetLastError();
             set_last_error("b200: selftest_expired_wait: set-up failed");
             return 4;
         }
+        note_foreign_enqueue((int)device);
         B200_LAUNCH(expired_wait_kernel, 1, 32, 0, (cudaStream_t)stream, status, 2000u);
         return cudaGetLastError() == cudaSuccess ? 0 : 4;
     } catch (...) {

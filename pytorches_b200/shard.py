@@ -57,6 +57,9 @@ def nccl_options():
     its CTA takes the first slot that frees up. ``PYTORCHES_B200_NCCL_PRIORITY=0`` turns that off."""
     import os
 
+    # The exchanges are a few bytes per rank: in-switch reduction gains nothing, and a rank that exits
+    # early while its memory is bound to an NVLink multicast object can fault its peers' GPUs.
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     ctas = int(os.environ.get("PYTORCHES_B200_NCCL_CTAS", "1"))
     high = os.environ.get("PYTORCHES_B200_NCCL_PRIORITY", "1") != "0"
     opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=high)
@@ -112,6 +115,9 @@ class ShardGroup:
             attach.restype, attach.argtypes = C.c_int32, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, C.c_uint32]
             reduce_.restype = C.c_int32
             reduce_.argtypes = [C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int64, C.c_uint64, C.c_void_p]
+            mean_ = lib.pytorches_b200_peer_mean
+            mean_.restype, mean_.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
+            self._peer_mean = mean_
             self.flush()
             handle = C.create_string_buffer(64)
             ok = export(self.device.index, handle) == 0
@@ -139,13 +145,28 @@ class ShardGroup:
     def peer_exchange(self) -> bool:
         return self._peer_reduce is not None
 
-    def _peer(self, kind: int, x_local: Tensor, first_index: int = 0) -> Tensor:
+    def _peer(self, kind: int, x_local: Tensor, first_index: int = 0, n_total: int = 0) -> Tensor:
+        """kind 0 sum, 1 max, 2 argmax, 3 mean (``n_total`` = element count of the whole tensor)."""
         dev = self.device
         out = Tensor(Buffer(dev, 1, 8 if kind == 2 else 4), [], dtype=DTYPE_I64 if kind == 2 else DTYPE_F32)
         seq, self._peer_seq = self._peer_seq, self._peer_seq + 1  # ranks issue the same reductions in the same order
-        dev.plugin.check(self._peer_reduce(dev.index, kind, x_local.buffer.ptr, x_local.numel(), first_index, seq, out.buffer.ptr),
-                         "sharded reduction with in-kernel exchange")
+        if kind == 3:
+            status = self._peer_mean(dev.index, x_local.buffer.ptr, x_local.numel(), n_total, seq, out.buffer.ptr)
+        else:
+            status = self._peer_reduce(dev.index, kind, x_local.buffer.ptr, x_local.numel(), first_index, seq, out.buffer.ptr)
+        dev.plugin.check(status, "sharded reduction with in-kernel exchange")
+        note = getattr(dev.plugin, "peer_reduce", None)  # a recorder writes the call down (replay.Recorder)
+        if note is not None:
+            note(dev.index, kind, x_local.buffer.ptr, x_local.numel(), first_index, n_total, out.buffer.ptr, out.dtype)
         return out
+
+    def advance_peer_seq(self, to: int) -> None:
+        """After a replayed list issued sharded reductions natively: the next one continues from ``to``."""
+        self._peer_seq = to
+
+    @property
+    def peer_seq(self) -> int:
+        return self._peer_seq
 
     # ---- plumbing ----
     def torch_view(self, t: Tensor) -> torch.Tensor:
@@ -232,8 +253,8 @@ class ShardGroup:
 
     def mean(self, x_local: Tensor, n_global: int) -> Tensor:
         """``Tensor.mean`` of the reference: the sum, then a DIV by the element count as a scalar tensor."""
-        if self._peer_reduce:
-            return self._peer(0, x_local).raw_binary(Tensor.scalar_on(float(n_global), self.device), op.DIV)
+        if self._peer_reduce:  # the DIV by the f32 count runs in the combining kernel: the same bits, one launch instead of three
+            return self._peer(3, x_local, 0, n_global)
 
         def finish(gathered, out_buf):
             total = gathered[0].raw_sum_axis(0)

@@ -41,6 +41,27 @@ def test_noalloc_sum_matches_sum_axis_on_consecutive_calls(b200):
         assert_bit_equal(f"noalloc sum n={n}", got.get(), want.get())
 
 
+def test_noalloc_sum_on_the_default_stream_and_leaves_the_current_device_alone(b200):
+    """``stream`` = NULL is CUDA's default stream. The call must not change the calling thread's
+    current device (a host framework set it for its own work)."""
+    import torch
+
+    fn, _ = _entry(b200)
+    n = 65536 * 11 + 321
+    x = Buf(b200, lcg_data(n, 31))
+    want = Buf.empty(b200, 1)
+    assert exec_op(b200, op.SUM_AXIS, [0], [(x, (n,), (1,))], want, ()) == abi.STATUS_OK, b200.last_error()
+    b200.synchronize(0)  # x is complete before a kernel on another stream reads it
+    before = torch.cuda.current_device()
+    got = Buf.empty(b200, 1)
+    b200.synchronize(0)
+    for _ in range(2):
+        assert fn(0, x.ptr, n, got.ptr, None) == abi.STATUS_OK, b200.last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.current_device() == before
+    assert_bit_equal("noalloc sum on the default stream", got.get(), want.get())
+
+
 def test_noalloc_sum_rejects_sizes_beyond_its_scratch(b200):
     fn, stream = _entry(b200)
     x = Buf(b200, lcg_data(64, 1))
