@@ -120,6 +120,19 @@ int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *
 int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, uint64_t n, uint64_t n_total, uint64_t seq, float *out);
 
 /*
+ * The same for a small vector result: the sum over the leading dimension of a [rows_total, cols]
+ * tensor whose rows are split over the ranks, e.g. the bias gradient the reference core computes by
+ * SUM_AXIS(0) when it reduces a broadcast gradient back to the bias's shape
+ * (crates/core/src/lib.rs:578-591). `x` = this rank's [rows, cols] rows (rows may differ between
+ * ranks, may be 0), `out` = cols f32 values: the per-rank column sums, exchanged through the windows
+ * (one self-validating word per element) and added in rank order on every rank, the bits SUM_AXIS(0)
+ * gives over the gathered [world, cols] tensor of per-rank sums. cols is at most 4096 (16 KiB of
+ * results); larger results are refused with PT_STATUS_INVALID_ARGUMENT and belong to a collective
+ * library. `seq` counts in the same sequence as the scalar reductions.
+ */
+int32_t pytorches_b200_peer_sum_axis0(uint32_t device, const float *x, uint64_t rows, uint64_t cols, uint64_t seq, float *out);
+
+/*
  * Replay of a recorded call list. The reference core issues one `execute` per tensor op, each with
  * an `alloc` for its result before and `free`s as tensors die (crates/core/src/lib.rs:331-370); a
  * training or benchmark step repeats the same list of calls every time. This entry point takes such

@@ -126,6 +126,10 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
 // Kernels with bounded device-side waits report an expired wait in a host-visible word, one per
 // device; this returns and clears it (0 = nothing happened).
 int take_reduce_status(int device);
+// The cross-GPU step for a vector result: every rank's `partial[0..m)` summed in rank order into
+// `out[0..m)` on every rank (m at most peer_vector_max()); see peer_vector_sum_kernel.
+cudaError_t launch_peer_vector_sum(const PeerXchg &px, const float *partial, uint64_t m, float *out, int device, cudaStream_t s);
+uint64_t peer_vector_max();
 // Per column of [g, m] candidates (value, position), the position of the best one.
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s);
 

@@ -234,13 +234,47 @@ template <typename I> struct Pack<I, 1> {
     __device__ __forceinline__ void load(const float *base, uint32_t istride, I c) { v = istride ? ld1(base + c) : __ldg(base); }
 };
 
-template <class Fn, typename I, int VEC>
+// WARPROW: the row length in items is a multiple of 128, so the 128 consecutive items a warp takes
+// (lane + 32 k, k = 0..3) lie in ONE row: the row is decomposed once per thread instead of once per
+// item, and an operand that is broadcast along the row (inner stride 0: a column vector) is loaded
+// once. Otherwise item k of a thread is 256 items further on and may sit in another row each time.
+template <class Fn, typename I, int VEC, bool WARPROW>
 __global__ void __launch_bounds__(EW_BLOCK) binary_rows_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                                float *__restrict__ out,
                                                                const __grid_constant__ RowsPlan<I, 2> p) {
-    const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
     Pack<I, VEC> va[EW_UNROLL], vb[EW_UNROLL];
     uint64_t oo[EW_UNROLL];
+    if constexpr (WARPROW) {
+        const I first = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + (I)((threadIdx.x >> 5) * (32 * EW_UNROLL) + (threadIdx.x & 31));
+        const bool live = first < p.items;  // items is a multiple of 128 here: a warp is live or not as a whole
+        if (live) {
+            I row, c;
+            p.cols.divmod(first, row, c);
+            uint64_t off[2];
+            rows_offsets<I, 2>(p, row, off);
+            const uint64_t o0 = (uint64_t)row * p.inner + (uint64_t)c * VEC;
+            Pack<I, VEC> sa, sb;
+            if (!p.istride[0]) sa.load(a + off[0], 0, c);
+            if (!p.istride[1]) sb.load(b + off[1], 0, c);
+#pragma unroll
+            for (int k = 0; k < EW_UNROLL; ++k) {
+                if (p.istride[0]) va[k].load(a + off[0], 1, c + (I)(32 * k)); else va[k] = sa;
+                if (p.istride[1]) vb[k].load(b + off[1], 1, c + (I)(32 * k)); else vb[k] = sb;
+                oo[k] = o0 + (uint64_t)(32 * k) * VEC;
+            }
+#pragma unroll
+            for (int k = 0; k < EW_UNROLL; ++k) {
+                if constexpr (VEC == 4) {
+                    const float4 x = va[k].v, y = vb[k].v;
+                    st4(out + oo[k], make_float4(Fn::f(x.x, y.x), Fn::f(x.y, y.y), Fn::f(x.z, y.z), Fn::f(x.w, y.w)));
+                } else {
+                    st1(out + oo[k], Fn::f(va[k].v, vb[k].v));
+                }
+            }
+        }
+        return;
+    }
+    const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
 #pragma unroll
     for (int k = 0; k < EW_UNROLL; ++k) {
         const I w = tile + (I)(k * EW_BLOCK);
@@ -821,14 +855,17 @@ template <class Fn> cudaError_t run_binary_body(const float *a, const float *b, 
         uint64_t rows = p.n / p.dim[p.nd - 1].size;
         const uint64_t items = rows * ((p.dim[p.nd - 1].size + vec - 1) / vec);
         const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
+        const bool warprow = vec == 4 && (p.dim[p.nd - 1].size / 4) % (32 * EW_UNROLL) == 0;  // a warp's 128 items share a row
         if (rows_plan_fits_32bit(items, p.dim[p.nd - 1].size)) {
             auto plan = make_rows_plan<uint32_t, 2>(p, vec);
-            if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            if (warprow) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
         } else {
             auto plan = make_rows_plan<uint64_t, 2>(p, vec);
-            if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            if (warprow) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
         }
         return cudaGetLastError();
     } else {

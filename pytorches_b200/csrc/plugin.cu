@@ -643,6 +643,33 @@ PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n,
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer reduce", e);
 }
 
+// Sum over the leading dimension of a [rows, m] tensor whose rows are split over the ranks: the local
+// SUM_AXIS(0) of this rank's rows, then the exchange and rank-ordered combine of the m partial sums.
+PtStatus peer_sum_axis0(uint32_t device, const float *x, uint64_t rows, uint64_t m, uint64_t seq, float *out) {
+    if (!out || (!x && rows && m)) B200_INVALID("b200: peer sum_axis0: null pointer");
+    if (m == 0 || m > peer_vector_max()) B200_INVALID("b200: peer sum_axis0: %llu columns (1 to %llu are exchanged inside the kernel)",
+                                                        (unsigned long long)m, (unsigned long long)peer_vector_max());
+    if (((uintptr_t)x & 3) || ((uintptr_t)out & 3)) B200_INVALID("b200: peer sum_axis0: pointers must be 4-byte aligned");
+    B200_ENTER(device);
+    PeerXchg px;
+    if (!peer_window_for((int)device, seq, &px)) B200_INVALID("b200: peer sum_axis0: no peer windows attached on device %u", device);
+    void *partial = nullptr, *scratch = nullptr;
+    PtStatus st = alloc_locked(d, m * sizeof(float), &partial);
+    if (st != PT_STATUS_OK) return st;
+    const size_t sb = reduce_scratch_bytes(REDUCE_SUM, 1, rows, m, (int)device);
+    if (sb && (st = alloc_locked(d, sb, &scratch)) != PT_STATUS_OK) {
+        free_locked(d, partial);
+        return st;
+    }
+    d.chain.tail_open = false;
+    cudaError_t e = launch_reduce(REDUCE_SUM, x, 1, rows, m, (float *)partial, nullptr, 0, scratch, (int)device, d.stream);
+    if (e == cudaSuccess) e = launch_peer_vector_sum(px, (const float *)partial, m, out, (int)device, d.stream);
+    d.chain.tail_open = false;
+    if (scratch) free_locked(d, scratch);
+    free_locked(d, partial);  // the stream orders any reuse behind the launches
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer sum_axis0", e);
+}
+
 // ---- replay of a recorded call list (extension entry point) --------------------------------------------------
 
 static_assert(sizeof(PtB200Operand) == 152 && sizeof(PtB200Call) == 656, "replay structs are part of the C ABI");
@@ -816,6 +843,15 @@ B200_EXPORT int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, ui
         return b200::peer_reduce(device, 3, x, n, 0, seq, out, (float)n_total);
     } catch (...) {
         b200::set_last_error("b200: peer mean raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_sum_axis0(uint32_t device, const float *x, uint64_t rows, uint64_t cols, uint64_t seq, float *out) {
+    try {
+        return b200::peer_sum_axis0(device, x, rows, cols, seq, out);
+    } catch (...) {
+        b200::set_last_error("b200: peer sum_axis0 raised an exception");
         return PT_STATUS_INTERNAL;
     }
 }

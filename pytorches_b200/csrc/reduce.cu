@@ -261,6 +261,55 @@ __global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant
     peer_finish(px, kind, v ? v[0] : 0.0f, i ? i[0] : (int64_t)px.rank, v, i, status);  // no position: the rank breaks ties
 }
 
+// ---- the cross-GPU step for small VECTOR results (a bias gradient: the sum over a sharded leading
+// dimension of a [rows, m] tensor, m up to PEER_VECTOR_MAX) ---------------------------------------------
+// The same idea as above, one word per element: thread j stores (epoch << 32) | bits(partial[j]) into
+// element j of slot `rank` of EVERY rank's window (plain peer stores; each 64-bit word validates
+// itself, so no ordering between words is needed), then polls element j of every rank's slot in its
+// OWN window until it carries this epoch, and adds the values in rank order from 0.0: what SUM_AXIS
+// over the gathered [world, m] tensor computes (reduce.rs:132-145), on every rank alike. The vector
+// area of a window follows its scalar area: PEER_GENERATIONS x PEER_MAX_RANKS slots of
+// PEER_VECTOR_MAX words, generations used in turn exactly as for scalars. Waits are bounded in time.
+constexpr uint32_t PEER_VECTOR_MAX = 4096;           // elements (16 KiB of f32)
+constexpr size_t PEER_VECTOR_AREA_WORD = 512;        // first word of the vector area (the scalar area ends before it)
+
+__global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_constant__ PeerXchg px, const float *__restrict__ partial, uint32_t m,
+                                                              float *__restrict__ out, int *status) {
+    const uint32_t j = blockIdx.x * 256 + threadIdx.x;
+    bool ok = true;
+    if (j < m) {
+        const size_t gen = PEER_VECTOR_AREA_WORD + (size_t)(px.epoch % PEER_GENERATIONS) * PEER_MAX_RANKS * PEER_VECTOR_MAX;
+        const unsigned long long w = ((unsigned long long)px.epoch << 32) | __float_as_uint(partial[j]);
+        unsigned long long *mine = px.window[0];
+#pragma unroll
+        for (int r = 0; r < PEER_MAX_RANKS; ++r) {
+            if (r < px.world) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(px.window[r] + gen + (size_t)px.rank * PEER_VECTOR_MAX + j), "l"(w) : "memory");
+            if (px.rank == r) mine = px.window[r];
+        }
+        const unsigned long long t0 = global_ns(), limit = (unsigned long long)px.wait_ms * 1000000ull;
+        float s = 0.0f;
+        for (int r = 0; r < px.world && ok; ++r) {
+            const unsigned long long *src = mine + gen + (size_t)r * PEER_VECTOR_MAX + j;
+            ok = false;
+            for (uint32_t tries = 0; tries < (1u << 30); ++tries) {  // the time limit ends the loop; the count is a second guard
+                unsigned long long got;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(src) : "memory");
+                if ((uint32_t)(got >> 32) == px.epoch) {
+                    s = __fadd_rn(s, __uint_as_float((uint32_t)got));
+                    ok = true;
+                    break;
+                }
+                if ((tries & 63) == 63 && global_ns() - t0 > limit) break;
+            }
+        }
+        if (ok) out[j] = s;
+    }
+    if (!ok) {
+        *(volatile int *)status = STATUS_PEER_WAIT_EXPIRED;
+        __threadfence_system();
+    }
+}
+
 // A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 256 words
 // per round (8 per lane, all in flight together) and re-polls only the ones not yet published.
 constexpr int COMBINER_WORDS = 8;
@@ -551,6 +600,144 @@ __global__ void __launch_bounds__(32) sum_cols_tma_kernel(const __grid_constant_
             mbar_expect_tx(&bars[st], COLS_TILE_BYTES);
             tile_load_2d(ring + (size_t)st * COLS_TILE_ROWS * 32, &map, (int32_t)c0, (int32_t)(row0 + (uint64_t)(t + COLS_STAGES) * COLS_TILE_ROWS), &bars[st]);
         }
+    }
+    if (lane < (int)ncols) out[o * inner + c0 + lane] = s;
+}
+
+// inner > 1, TMA-staged, chains fed by ldmatrix: the form that brings a column's chain down to the add
+// latency. In the kernel above the warp that owns the chains fetches every row with one 4-byte
+// shared-memory load, and a lone warp cannot issue a load and a dependent add in the same four
+// cycles: 5.1 to 6.3 cycles per row measured on the bare loop, 7.5 in that kernel, against 4.07 for the
+// dependent adds alone. What the chain of column c needs is rows r, r+1, r+2, r+3 of column c in four
+// registers of lane c. That is exactly what ldmatrix.x4 delivers when it is pointed at four
+// consecutive 128-byte rows of the row-major tile as the TMA engine lands it: a "matrix" of eight
+// 16-byte rows is one 128-byte tile row (eight chunks of four columns), and the instruction hands
+// thread T the 32-bit element (matrix row T / 4, position T % 4), i.e. column 4 (T / 4) + T % 4 = T of that
+// tile row. One instruction per four rows, no transposition, no extra shared-memory traffic: 4.29
+// cycles per row measured on the bare loop.
+//   * warp 1, one lane (producer): keeps STAGES tile copies of [128 rows x 32 columns] in flight and
+//     refills a stage when the chain warp has released it;
+//   * warp 0 (chains): adds the rows of its column in row order from 0.0 as the reference does
+//     (reduce.rs:132-145), sixteen rows of loads always in flight ahead of the adds, across tile
+//     boundaries too.
+// Every wait is bounded; a wait that runs out is reported through *status, the copies that may still
+// be in flight get the same bounded chance to land, and the CTA exits without a result.
+constexpr size_t ldm_smem(int stages, int rows) { return 128 /* alignment slack */ + (size_t)stages * rows * 128 + 2 * stages * sizeof(uint64_t) + 16; }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+// Rows r .. r+3 of the lane's column, from four consecutive 128-byte rows of a row-major f32 tile:
+// `addr` = tile row r + lane / 8, 16-byte chunk lane % 8 (the row address every thread supplies).
+__device__ __forceinline__ float4 ldmatrix_rows4(uint32_t addr) {
+    float4 v;
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+
+template <int STAGES, int LDM_ROWS>
+__global__ void __launch_bounds__(64) sum_cols_ldm_kernel(const __grid_constant__ CUtensorMap map, uint64_t len, uint64_t inner,
+                                                          uint32_t groups_per_outer, float *__restrict__ out, int *status) {
+    constexpr uint32_t LDM_TILE_BYTES = LDM_ROWS * 32 * sizeof(float);
+    extern __shared__ unsigned char ldm_raw[];
+    const uint32_t base = (smem_addr(ldm_raw) + 127u) & ~127u;
+    unsigned char *aligned = ldm_raw + (base - smem_addr(ldm_raw));
+    float *ring = reinterpret_cast<float *>(aligned);  // [STAGES][128][32]
+    uint64_t *full = reinterpret_cast<uint64_t *>(aligned + (size_t)STAGES * LDM_TILE_BYTES), *empty = full + STAGES;
+    volatile int *failed = reinterpret_cast<volatile int *>(empty + STAGES);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2 * STAGES; ++i) mbar_init(&full[i], 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint64_t o = blockIdx.x / groups_per_outer;
+    const uint32_t c0 = (blockIdx.x % groups_per_outer) * 32;
+    const uint32_t ncols = inner - c0 < 32 ? (uint32_t)(inner - c0) : 32;
+    const uint64_t row0 = o * len;
+    const uint32_t tiles = (uint32_t)((len + LDM_ROWS - 1) / LDM_ROWS), full_tiles = (uint32_t)(len / LDM_ROWS);
+
+    if (warp == 1) {
+        // ---- producer: one lane ----
+        if (lane != 0) return;
+        for (uint32_t t = 0; t < tiles; ++t) {
+            const int st = t % STAGES;
+            if (t >= (uint32_t)STAGES && !mbar_wait_bounded(&empty[st], ((t / STAGES) - 1) & 1)) {
+                *failed = 1;
+                *(volatile int *)status = STATUS_WAIT_EXPIRED;
+                __threadfence_system();
+                return;
+            }
+            if (*failed) return;
+            mbar_expect_tx(&full[st], LDM_TILE_BYTES);
+            tile_load_2d(ring + (size_t)st * LDM_ROWS * 32, &map, (int32_t)c0, (int32_t)(row0 + (uint64_t)t * LDM_ROWS), &full[st]);
+        }
+        return;
+    }
+
+    // ---- chains ----
+    const uint32_t lane_off = (uint32_t)(lane >> 3) * 128 + (uint32_t)(lane & 7) * 16;
+    constexpr uint32_t NONE = 0xffffffffu;
+    uint32_t gave_up_at = NONE;  // the tile whose wait ran out, if any
+    float s = 0.0f;
+    float4 v[2][4];  // two batches of sixteen rows: one being added, one in flight
+    if (full_tiles > 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full[0], 0))) gave_up_at = 0;
+        const uint32_t a0 = smem_addr(ring) + lane_off;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[0][u] = ldmatrix_rows4(a0 + 4 * u * 128);
+    }
+    for (uint32_t t = 0; t < full_tiles && gave_up_at == NONE; ++t) {
+        const uint32_t a = smem_addr(ring + (size_t)(t % STAGES) * LDM_ROWS * 32) + lane_off;
+        const uint32_t nt = t + 1;
+        bool next_landed = false;
+#pragma unroll
+        for (int bb = 0; bb < LDM_ROWS / 16; ++bb) {
+            // One look at the next tile's barrier well before it is needed: the answer is back by the time
+            // the last batch of this tile is reached, and the wait below is then skipped.
+            if (bb == LDM_ROWS / 16 - 3 && nt < full_tiles) next_landed = mbar_try_wait(&full[nt % STAGES], (nt / STAGES) & 1);
+            if (bb + 1 < LDM_ROWS / 16) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[(bb + 1) & 1][u] = ldmatrix_rows4(a + (16 * (bb + 1) + 4 * u) * 128);
+            } else if (nt < full_tiles) {  // the next tile's first sixteen rows (it has normally landed long ago)
+                if (!__all_sync(0xffffffffu, next_landed) && !__all_sync(0xffffffffu, mbar_wait_bounded(&full[nt % STAGES], (nt / STAGES) & 1)))
+                    gave_up_at = nt;
+                const uint32_t an = smem_addr(ring + (size_t)(nt % STAGES) * LDM_ROWS * 32) + lane_off;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[0][u] = ldmatrix_rows4(an + 4 * u * 128);  // harmless if the wait ran out: the result is dropped
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                s = __fadd_rn(s, v[bb & 1][u].x);
+                s = __fadd_rn(s, v[bb & 1][u].y);
+                s = __fadd_rn(s, v[bb & 1][u].z);
+                s = __fadd_rn(s, v[bb & 1][u].w);
+            }
+        }
+        __syncwarp();  // every lane has its last rows of this stage in registers
+        if (lane == 0) mbar_arrive(&empty[t % STAGES]);
+    }
+    if (full_tiles < tiles && gave_up_at == NONE) {  // the last, partial tile: row by row (rows past the end were zero-filled and are not added)
+        const uint32_t t = full_tiles;
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full[t % STAGES], (t / STAGES) & 1))) {
+            gave_up_at = t;
+        } else {
+            const float *buf = ring + (size_t)(t % STAGES) * LDM_ROWS * 32 + lane;
+            const uint32_t rows = (uint32_t)(len - (uint64_t)t * LDM_ROWS);
+            for (uint32_t r = 0; r < rows; ++r) s = __fadd_rn(s, buf[r * 32]);
+        }
+    }
+    if (gave_up_at != NONE) {
+        // A wait that ran out: tell the producer, give the copies it may have issued (at most STAGES - 1
+        // tiles past that one) their bounded chance to land, report, leave without a result.
+        if (lane == 0) *failed = 1;
+        for (uint32_t d = gave_up_at + 1; d < tiles && d < gave_up_at + STAGES; ++d) (void)mbar_wait_bounded(&full[d % STAGES], (d / STAGES) & 1);
+        if (lane == 0) {
+            *(volatile int *)status = STATUS_WAIT_EXPIRED;
+            __threadfence_system();
+        }
+        return;
     }
     if (lane < (int)ncols) out[o * inner + c0 + lane] = s;
 }
@@ -974,7 +1161,9 @@ bool staged_kernels_ready(int device) {
 #undef B200_RING_ATTR
         ok[device] = good &&
                      cudaFuncSetAttribute(sum_cols_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(128)) == cudaSuccess &&
-                     cudaFuncSetAttribute(sum_cols_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(256)) == cudaSuccess;
+                     cudaFuncSetAttribute(sum_cols_tma_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cols_smem(256)) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_cols_ldm_kernel<4, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ldm_smem(4, 256)) == cudaSuccess &&
+                     cudaFuncSetAttribute(sum_cols_ldm_kernel<4, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ldm_smem(4, 128)) == cudaSuccess;
         if (!ok[device]) (void)cudaGetLastError();
     }
     return ok[device];
@@ -1009,12 +1198,14 @@ bool make_cols_tensor_map(CUtensorMap *map, const float *x, uint64_t rows, uint6
 
 // ---- peer windows ------------------------------------------------------------------------------------------
 // One window per device of this process: a 2 MiB allocation of its own (so that its IPC handle shares
-// a driver allocation with nothing else), of which the first PEER_WINDOW_WORDS words are used. It is
+// a driver allocation with nothing else): the scalar slots, then the vector area (see peer_vector_sum_kernel). It is
 // created and zeroed by the first export and kept for the life of the process; every export zeroes it
 // again, so that epochs may restart with a new group of ranks. Peers' windows are opened once per
 // handle and never closed.
 namespace {
 constexpr size_t PEER_WINDOW_BYTES = size_t(2) << 20;
+static_assert(PEER_WINDOW_WORDS <= PEER_VECTOR_AREA_WORD, "the scalar slots end before the vector area");
+static_assert((PEER_VECTOR_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_VECTOR_MAX) * 8 <= PEER_WINDOW_BYTES, "the vector area fits the window");
 struct PeerWindows {
     std::mutex mu;
     unsigned long long *local[64] = {};
@@ -1196,6 +1387,21 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
             CUtensorMap map;
             int *status = reduce_status_word(device);
             const unsigned ctas = (unsigned)(outer * groups_per_outer);
+            // PYTORCHES_B200_SUM_COLS=plain keeps the one-warp form (diagnostic, read once).
+            static const bool matrix_loads = [] {
+                const char *e = getenv("PYTORCHES_B200_SUM_COLS");
+                return !(e && e[0] == 'p');
+            }();
+            // One CTA per SM can afford tall tiles (256 rows, 32 KiB each, 128 KiB in flight), which halve the
+            // per-tile bookkeeping of the chain warp; with more column groups than SMs, three CTAs share an SM.
+            const bool tall_tiles = ctas <= (unsigned)sm_count(device) && len >= 1024;
+            if (matrix_loads && status && make_cols_tensor_map(&map, x, outer * len, inner, tall_tiles ? 256 : 128)) {
+                if (tall_tiles)
+                    B200_LAUNCH((sum_cols_ldm_kernel<4, 256>), ctas, 64, ldm_smem(4, 256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                else
+                    B200_LAUNCH((sum_cols_ldm_kernel<4, 128>), ctas, 64, ldm_smem(4, 128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                return cudaGetLastError();
+            }
             const bool tall = ctas < 2u * (unsigned)sm_count(device) && len >= 1024;
             if (status && make_cols_tensor_map(&map, x, outer * len, inner, tall ? 256 : 128)) {
                 if (tall) B200_LAUNCH(sum_cols_tma_kernel<256>, ctas, 32, cols_smem(256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
@@ -1285,6 +1491,16 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
     B200_LAUNCH(peer_exchange_kernel, 1, 32, 0, s, *px, (int)kind, out_v, kind == REDUCE_MAX_ARGMAX ? out_i : (int64_t *)nullptr, status);
     return cudaGetLastError();
 }
+
+cudaError_t launch_peer_vector_sum(const PeerXchg &px, const float *partial, uint64_t m, float *out, int device, cudaStream_t s) {
+    if (px.world <= 0 || m == 0 || m > PEER_VECTOR_MAX) return cudaErrorInvalidValue;
+    int *status = reduce_status_word(device);
+    if (!status) return cudaErrorMemoryAllocation;
+    B200_LAUNCH(peer_vector_sum_kernel, (unsigned)((m + 255) / 256), 256, 0, s, px, partial, (uint32_t)m, out, status);
+    return cudaGetLastError();
+}
+
+uint64_t peer_vector_max() { return PEER_VECTOR_MAX; }
 
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s) {
     B200_LAUNCH(argmax_combine_kernel, (unsigned)((m + 255) / 256), 256, 0, s, vals, idx, g, m, out);

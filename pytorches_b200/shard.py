@@ -118,6 +118,9 @@ class ShardGroup:
             mean_ = lib.pytorches_b200_peer_mean
             mean_.restype, mean_.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
             self._peer_mean = mean_
+            vec_ = lib.pytorches_b200_peer_sum_axis0
+            vec_.restype, vec_.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
+            self._peer_sum_axis0 = vec_
             self.flush()
             handle = C.create_string_buffer(64)
             ok = export(self.device.index, handle) == 0
@@ -241,8 +244,20 @@ class ShardGroup:
             run_op_into(self.device, code, [0], [Operand.contiguous(g)], out_buf, g.shape[1:], out_dtype)
         return finish
 
+    PEER_VECTOR_MAX = 4096  # elements of a result the in-kernel exchange carries (pytorches_b200_peer_sum_axis0)
+
     def sum_axis0(self, x_local: Tensor) -> Tensor:
-        """Sum over the sharded leading dimension: local SUM_AXIS(0), all-gather, SUM_AXIS(0) in rank order."""
+        """Sum over the sharded leading dimension: local SUM_AXIS(0), all-gather, SUM_AXIS(0) in rank order.
+        With the in-kernel exchange enabled and a result of at most 4096 elements (a bias gradient), the
+        per-rank sums travel through the peer windows instead and no collective library is involved."""
+        m = math.prod(x_local.shape[1:])
+        if self._peer_reduce and 0 < m <= self.PEER_VECTOR_MAX:
+            dev = self.device
+            out = Tensor(Buffer(dev, m), list(x_local.shape[1:]))
+            seq, self._peer_seq = self._peer_seq, self._peer_seq + 1
+            dev.plugin.check(self._peer_sum_axis0(dev.index, x_local.buffer.ptr, x_local.shape[0] if x_local.shape else 1, m, seq, out.buffer.ptr),
+                             "sharded column sum with in-kernel exchange")
+            return out
         return self._defer(lambda: [x_local.raw_sum_axis(0)], x_local.shape[1:], DTYPE_F32, self._combine(op.SUM_AXIS))
 
     def sum(self, x_local: Tensor) -> Tensor:

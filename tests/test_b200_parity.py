@@ -20,6 +20,7 @@ import pytest
 from harness import Buf, assert_bit_equal, exec_op, lcg_data, ulp_distance
 from pytorches_b200 import abi
 from pytorches_b200.abi import DTYPE_I64, contiguous_strides, op
+from pytorches_b200 import synth
 from pytorches_b200.core import SGD, Device, Tensor, mse_loss
 
 pytestmark = pytest.mark.gpu
@@ -194,7 +195,9 @@ def test_axpy_bit_exact(oracle, b200, n):
 
 
 SUM_CASES = [(1000,), (33, 17), (5, 4, 3), (70_001,), (3, 200_000), (100_000, 3), (2, 600, 5), (4, 4096, 70), (1, 1), (64, 4096),
-             (300, 64), (2, 1000, 36), (1, 129, 32), (5000, 128), (31,), (32,), (33,), (65536,), (65537,), (65536 * 5 + 77,), (4096, 4096), (1 << 22,), (128, 2048)]
+             (300, 64), (2, 1000, 36), (1, 129, 32), (5000, 128), (31,), (32,), (33,), (65536,), (65537,), (65536 * 5 + 77,), (4096, 4096), (1 << 22,), (128, 2048),
+             # column sums through the transposing kernel: ragged tiles, ragged column groups, several slabs, many tiles
+             (1000, 96), (3, 257, 160), (520, 40), (16384, 256), (127, 64), (128, 32), (129, 4100), (2, 385, 36), (40_000, 32)]
 
 
 @pytest.mark.parametrize("shape", SUM_CASES)
@@ -245,6 +248,12 @@ def test_fill_and_randn(oracle, b200):
         assert_bit_equal(f"fill n={n}", got, want)
         got, want = both(oracle, b200, op.RAND_NORMAL, [1234], [], (n,))
         assert np.max(np.abs(got - want)) <= 1e-5, f"randn n={n}: {np.max(np.abs(got - want))}"
+        # RAND_UNIFORM (appended): hash, one multiply, one add; exact on both sides and equal to the numpy generator
+        for lo, hi, first in ((-1.0, 1.0, 0), (0.5, 2.0, 1 << 33)):
+            ints = [31, f32_bits(lo), f32_bits(hi - lo), first]
+            got, want = both(oracle, b200, op.RAND_UNIFORM, ints, [], (n,))
+            assert_bit_equal(f"rand_uniform n={n}", got, want)
+            assert_bit_equal(f"rand_uniform n={n} vs numpy", got, synth.uniform(n, 31, lo, hi, first))
 
 
 # ---- the benchmark configurations, at sizes the oracle finishes in seconds, through the mini-core ----
@@ -305,7 +314,7 @@ def test_config4_softmax_from_primitives(oracle, b200, transposed):
     cpu = Device(oracle, 0)
     X0 = Tensor.randn_on([B, R, Cn], 21, cpu).numpy() * np.float32(2.0)
     m10 = Tensor.randn_on([B, 1, Cn], 22, cpu).numpy()
-    m20 = np.where(lcg_data(R, 23) < -0.8, np.float32(-1e4), np.float32(0.0)).astype(np.float32).reshape(1, R, 1)
+    m20 = synth.softmax_mask(R)
 
     def step(dev):
         m1, m2 = Tensor.from_numpy(m10, dev), Tensor.from_numpy(m20, dev)
@@ -371,7 +380,7 @@ def test_config4_full_size_bit_exact(oracle, b200):
     cpu = Device(oracle, 0)
     X0 = Tensor.randn_on([B, R, Cn], 21, cpu).numpy() * np.float32(2.0)
     m10 = Tensor.randn_on([B, 1, Cn], 22, cpu).numpy()
-    m20 = np.where(lcg_data(R, 23) < -0.8, np.float32(-1e4), np.float32(0.0)).astype(np.float32).reshape(1, R, 1)
+    m20 = synth.softmax_mask(R)
 
     def step(dev):
         Y = Tensor.from_numpy(X0, dev) + Tensor.from_numpy(m10, dev) + Tensor.from_numpy(m20, dev)
@@ -390,8 +399,9 @@ def test_config4_full_size_bit_exact(oracle, b200):
 
 
 def test_config2_full_size_against_oracle(oracle, b200):
-    """2^28 elements: sum and mean bit-equal to the oracle's, max and argmax exact."""
-    x0 = Tensor.randn_on([1 << 28], 7, Device(oracle, 0)).numpy()
+    """The benchmark's own tensor, 2^28 elements uniform[-1, 1) from seed 7: sum and mean bit-equal to the
+    oracle's, max and argmax exact."""
+    x0 = synth.uniform_pm1(1 << 28, 7)
 
     def step(dev):
         x = Tensor.from_numpy(x0, dev)

@@ -34,6 +34,34 @@ def test_single_rank_group_gives_the_plain_results(b200, n):
         assert g.argmax(t, 1000).numpy() == n // 3 + 1000
 
 
+@pytest.mark.parametrize("rows,cols", [(37, 24), (1000, 4096), (0, 64), (5, 1), (300, 1000)])
+def test_single_rank_group_column_sums_through_the_window(b200, rows, cols):
+    """A vector result (a bias gradient) goes through the window's vector area and back: the bits of SUM_AXIS(0)."""
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange(), b200.last_error()
+    x = lcg_data(rows * cols, 5).reshape(rows, cols)
+    t = Tensor.from_numpy(x, dev)
+    want = t.raw_sum_axis(0).numpy() if rows else np.zeros(cols, dtype=np.float32)
+    for _ in range(6):  # more than there are slot generations
+        got = g.sum_axis0(t).numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_column_sums_wider_than_the_window_are_refused(b200):
+    import ctypes as C
+
+    fn = b200.lib.pytorches_b200_peer_sum_axis0
+    fn.restype, fn.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange()
+    t = Tensor.from_numpy(lcg_data(2 * 4097, 1).reshape(2, 4097), dev)
+    out = Tensor.zeros_on([4097], dev)
+    assert fn(0, t.buffer.ptr, 2, 4097, 0, out.buffer.ptr) == abi.STATUS_INVALID_ARGUMENT and "4096" in b200.last_error()
+    assert g.sum_axis0(t).numpy().shape == (4097,)  # the shard layer falls back to its gather-and-combine path
+
+
 def test_a_peer_that_never_answers_is_a_reported_error_not_a_hang(b200):
     import ctypes as C
 

@@ -108,6 +108,13 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
         out_full = (Tensor.from_numpy(A, dev) + Tensor.from_numpy(b, dev)).relu() * Tensor.from_numpy(s_col, dev)
         assert np.array_equal(bits(out_local.numpy()), bits(out_full.numpy()[r0:r0 + rc]))
         db = g.sum_axis0(out_local).numpy()
+        if backend == "nccl":  # the same column sum with its exchange inside the kernel: the NCCL path's bits, several in a row
+            assert g.enable_peer_exchange(), gdev.plugin.last_error()
+            for _ in range(5):
+                assert np.array_equal(bits(g.sum_axis0(out_local).numpy()), bits(db))
+            wide = Tensor.from_numpy(np.tile(out_local.numpy(), (1, 170)), gdev)  # 4080 columns: nearly the largest result the windows carry
+            assert wide.shape[1] == 4080 and np.array_equal(bits(g.sum_axis0(wide).numpy()), bits(np.tile(db, 170)))
+            g.disable_peer_exchange()
         parts = []
         for r in range(world):
             s, c = split_rows(rows, r, world)
@@ -118,6 +125,39 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
         assert np.allclose(db, out_full.numpy().astype(np.float64).sum(axis=0), rtol=0, atol=1e-5 * np.abs(out_full.numpy()).sum(axis=0).max())
     finally:
         dist.destroy_process_group()
+
+
+def _layer_worker(rank: int, world: int, port: int):
+    """Config 3 with its layers dealt to the ranks: the union of the ranks' updated parameters must be
+    the single-device step's parameters, bit for bit (the placement it follows:
+    crates/core/src/strategy.rs:269-326; the update: crates/python/python/pytorches/optim.py:13-16)."""
+    sys.path.insert(0, ROOT)
+    os.environ["PYTORCHES_CPU_THREADS"] = "2"
+    from pytorches_b200.abi import Plugin
+    from pytorches_b200.configs import config3_sharded, split_layers_of
+    from pytorches_b200.core import Device
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        dev = Device(Plugin(ORACLE_SO), 0)
+        layers, width, batch = 5, 96, 8  # uneven over 2 and 3 ranks
+        _, _, mine = config3_sharded(dev, rank, world, layers, width, batch)()
+        _, _, every = config3_sharded(dev, 0, 1, layers, width, batch)()
+        own = split_layers_of(layers, rank, world)
+        assert len(mine) == 2 * len(own)
+        for k, l in enumerate(own):
+            for j in range(2):  # weight, bias
+                assert mine[2 * k + j].numpy().tobytes() == every[2 * l + j].numpy().tobytes(), f"layer {l} tensor {j}"
+        counts = [None] * world
+        dist.all_gather_object(counts, len(mine))
+        assert sum(counts) == 2 * layers  # every parameter tensor has exactly one owner
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_layer_sharded_sgd_over_gloo(oracle, world):
+    mp.spawn(_layer_worker, args=(world, _free_port()), nprocs=world, join=True)
 
 
 @pytest.mark.parametrize("world,n", [(2, 200_001), (3, 70_000)])
