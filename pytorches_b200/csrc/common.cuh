@@ -142,6 +142,26 @@ cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_
         ::b200::g_kernel_launches.fetch_add(1, std::memory_order_relaxed);          \
     } while (0)
 
+// Every kernel of this library that is not one of the chained reductions starts with ordered_start():
+// it may be SCHEDULED while the kernel before it in the stream is still draining (launch latency, CTA
+// set-up and parameter loads overlap that kernel's tail), but it touches no memory before that kernel
+// has completed and its writes are visible, so results and their order are those of plain stream
+// order. It then lets the kernel after it be scheduled the same way. Launched the ordinary way, both
+// instructions return at once.
+namespace b200 {
+__device__ __forceinline__ void ordered_start() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Whether kernels are launched for early scheduling at all (PYTORCHES_B200_OVERLAP=0 turns it off).
+bool overlap_enabled();
+}  // namespace b200
+
+// Launch of a kernel that begins with ordered_start().
+#define B200_LAUNCH_ORDERED(kernel, grid, block, smem, stream, ...) \
+    B200_LAUNCH_OVERLAP(::b200::overlap_enabled(), kernel, grid, block, smem, stream, __VA_ARGS__)
+
 // The same, optionally with programmatic stream serialization: the kernel may start once every CTA of
 // the kernel before it in the stream has signalled (griddepcontrol.launch_dependents) or exited,
 // instead of after that kernel has completed. Only for kernels written for it (see LaunchChain).

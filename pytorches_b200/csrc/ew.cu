@@ -136,6 +136,7 @@ inline unsigned tiles_for(uint64_t items, int per_cta) { return (unsigned)((item
 template <class Fn, int MODE>
 __global__ void __launch_bounds__(EW_BLOCK) binary_flat_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                                float *__restrict__ out, uint64_t n) {
+    ordered_start();
     const uint64_t items = (n + 3) >> 2;
     const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
     float4 va[EW_UNROLL], vb[EW_UNROLL];
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(EW_BLOCK) binary_flat_kernel(const float *__re
 template <class Fn>
 __global__ void __launch_bounds__(EW_BLOCK) unary_flat_kernel(const float *__restrict__ x, float *__restrict__ out, uint64_t n,
                                                               uint64_t n_poly) {
+    ordered_start();
     const uint64_t items = (n + 3) >> 2;
     const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
     float4 v[EW_UNROLL];
@@ -242,6 +244,7 @@ template <class Fn, typename I, int VEC, bool WARPROW>
 __global__ void __launch_bounds__(EW_BLOCK) binary_rows_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                                float *__restrict__ out,
                                                                const __grid_constant__ RowsPlan<I, 2> p) {
+    ordered_start();
     Pack<I, VEC> va[EW_UNROLL], vb[EW_UNROLL];
     uint64_t oo[EW_UNROLL];
     if constexpr (WARPROW) {
@@ -305,6 +308,7 @@ __global__ void __launch_bounds__(EW_BLOCK) binary_rows_kernel(const float *__re
 template <class Fn, typename I, int VEC>
 __global__ void __launch_bounds__(EW_BLOCK) unary_rows_kernel(const float *__restrict__ x, float *__restrict__ out,
                                                               const __grid_constant__ RowsPlan<I, 1> p, const LibmSplit split) {
+    ordered_start();
     const I tile = (I)blockIdx.x * (I)(EW_BLOCK * EW_UNROLL) + threadIdx.x;
     Pack<I, VEC> v[EW_UNROLL];
     uint64_t oo[EW_UNROLL];
@@ -361,6 +365,7 @@ template <class Fn, int NOPS>
 __global__ void __launch_bounds__(TILE *TILE_ROWS) tile_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                                float *__restrict__ out,
                                                                const __grid_constant__ TilePlan<NOPS> p, const LibmSplit split) {
+    ordered_start();
     __shared__ float sm[NOPS][TILE][TILE + 1];
     const float *src[2] = {a, b};
     // blockIdx.x enumerates (batch, tile_f, tile_i) with tile_i fastest.
@@ -434,6 +439,7 @@ template <int NOPS> struct WideTilePlan {
 template <class Fn, int NOPS>
 __global__ void __launch_bounds__(256) wide_tile_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
                                                         const __grid_constant__ WideTilePlan<NOPS> p, const LibmSplit split) {
+    ordered_start();
     __shared__ float sm[NOPS][WT][WT + 1];
     const float *src[2] = {a, b};
     const uint32_t ti = blockIdx.x % p.tiles_i, tf = blockIdx.x / p.tiles_i;
@@ -523,6 +529,7 @@ template <class Fn, int NOPS>
 __global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                                           float *__restrict__ out, const __grid_constant__ GatherPlan<NOPS> p,
                                                           const LibmSplit split) {
+    ordered_start();
     const uint64_t i = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
     if (i >= p.n) return;
     uint64_t rem = i, off[NOPS];
@@ -543,6 +550,7 @@ __global__ void __launch_bounds__(EW_BLOCK) gather_kernel(const float *__restric
 template <class Fn>
 __global__ void __launch_bounds__(32) binary_tail_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out,
                                                          const __grid_constant__ GatherPlan<2> p, uint64_t first) {
+    ordered_start();
     const uint64_t i = first + threadIdx.x;
     if (i >= p.n) return;
     uint64_t rem = i, off[2] = {0, 0};
@@ -561,6 +569,7 @@ __global__ void __launch_bounds__(32) binary_tail_kernel(const float *__restrict
 // the last n mod 8, which it computes with two roundings (plugins/cpu/src/ew.rs:316-329; its chunks
 // of 65536 are multiples of 8, so only the global tail is unfused). `out` may alias `a`.
 __global__ void __launch_bounds__(EW_BLOCK) axpy_kernel(const float *a, const float *b, float *out, float alpha, uint64_t n) {
+    ordered_start();
     const uint64_t n_fused = n - (n & 7);
     const uint64_t items = (n + 3) >> 2;
     const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
@@ -596,6 +605,7 @@ __global__ void __launch_bounds__(EW_BLOCK) axpy_kernel(const float *a, const fl
 }
 
 __global__ void __launch_bounds__(EW_BLOCK) fill_kernel(float *__restrict__ out, uint64_t n, float v) {
+    ordered_start();
     const uint64_t items = (n + 3) >> 2;
     const uint64_t tile = (uint64_t)blockIdx.x * (EW_BLOCK * EW_UNROLL) + threadIdx.x;
 #pragma unroll
@@ -627,6 +637,7 @@ __device__ __forceinline__ float rand_normal(uint64_t seed, uint64_t i) {
 }
 
 __global__ void __launch_bounds__(EW_BLOCK) randn_kernel(float *__restrict__ out, uint64_t n, uint64_t seed) {
+    ordered_start();
     const uint64_t items = (n + 3) >> 2;
     const uint64_t w = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
     if (w >= items) return;
@@ -647,6 +658,7 @@ __device__ __forceinline__ float rand_uniform(uint64_t seed, uint64_t i, float l
 
 __global__ void __launch_bounds__(EW_BLOCK) rand_uniform_kernel(float *__restrict__ out, uint64_t n, uint64_t seed, float lo, float scale,
                                                                 uint64_t first) {
+    ordered_start();
     const uint64_t items = (n + 3) >> 2;
     const uint64_t w = (uint64_t)blockIdx.x * EW_BLOCK + threadIdx.x;
     if (w >= items) return;
@@ -664,6 +676,7 @@ __global__ void __launch_bounds__(EW_BLOCK) rand_uniform_kernel(float *__restric
 __global__ void __launch_bounds__(TILE *TILE) matmul_kernel(const float *__restrict__ a, uint64_t ars, uint64_t acs,
                                                              const float *__restrict__ b, uint64_t brs, uint64_t bcs,
                                                              float *__restrict__ c, uint64_t m, uint64_t n, uint64_t k, uint32_t tiles_n) {
+    ordered_start();
     __shared__ float sa[TILE][TILE + 1], sb[TILE][TILE + 1];
     // Tiles are numbered along one grid axis (row-major), which has room for 2^31 - 1 of them.
     const uint32_t tile_row = blockIdx.x / tiles_n, tile_col = blockIdx.x - tile_row * tiles_n;
@@ -843,10 +856,10 @@ template <class Fn> cudaError_t run_binary_body(const float *a, const float *b, 
             const unsigned grid = tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL);
             const int mode = (sa ? 0 : 2) | (sb ? 0 : 1);
             switch (mode) {
-                case 0: B200_LAUNCH((binary_flat_kernel<Fn, 0>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
-                case 1: B200_LAUNCH((binary_flat_kernel<Fn, 1>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
-                case 2: B200_LAUNCH((binary_flat_kernel<Fn, 2>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
-                default: B200_LAUNCH((binary_flat_kernel<Fn, 3>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                case 0: B200_LAUNCH_ORDERED((binary_flat_kernel<Fn, 0>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                case 1: B200_LAUNCH_ORDERED((binary_flat_kernel<Fn, 1>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                case 2: B200_LAUNCH_ORDERED((binary_flat_kernel<Fn, 2>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
+                default: B200_LAUNCH_ORDERED((binary_flat_kernel<Fn, 3>), grid, EW_BLOCK, 0, s, a, b, out, p.n); break;
             }
             return cudaGetLastError();
         }
@@ -858,32 +871,32 @@ template <class Fn> cudaError_t run_binary_body(const float *a, const float *b, 
         const bool warprow = vec == 4 && (p.dim[p.nd - 1].size / 4) % (32 * EW_UNROLL) == 0;  // a warp's 128 items share a row
         if (rows_plan_fits_32bit(items, p.dim[p.nd - 1].size)) {
             auto plan = make_rows_plan<uint32_t, 2>(p, vec);
-            if (warprow) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else B200_LAUNCH((binary_rows_kernel<Fn, uint32_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            if (warprow) B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint32_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else if (vec == 4) B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint32_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint32_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
         } else {
             auto plan = make_rows_plan<uint64_t, 2>(p, vec);
-            if (warprow) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else if (vec == 4) B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
-            else B200_LAUNCH((binary_rows_kernel<Fn, uint64_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            if (warprow) B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint64_t, 4, true>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else if (vec == 4) B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint64_t, 4, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
+            else B200_LAUNCH_ORDERED((binary_rows_kernel<Fn, uint64_t, 1, false>), grid, EW_BLOCK, 0, s, a, b, out, plan);
         }
         return cudaGetLastError();
     } else {
         WideTilePlan<2> w{};
         dim3 wgrid;
         if (make_wide_tile_plan<2>(p, w, wgrid)) {
-            B200_LAUNCH((wide_tile_kernel<Fn, 2>), wgrid, 256, 0, s, a, b, out, w, LibmSplit{});
+            B200_LAUNCH_ORDERED((wide_tile_kernel<Fn, 2>), wgrid, 256, 0, s, a, b, out, w, LibmSplit{});
             return cudaGetLastError();
         }
         TilePlan<2> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<2>(p, t, ctas)) {
-            B200_LAUNCH((tile_kernel<Fn, 2>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, a, b, out, t, LibmSplit{});
+            B200_LAUNCH_ORDERED((tile_kernel<Fn, 2>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, a, b, out, t, LibmSplit{});
             return cudaGetLastError();
         }
     }
     auto g = make_gather_plan<2>(p);
-    B200_LAUNCH((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g, LibmSplit{});
+    B200_LAUNCH_ORDERED((gather_kernel<Fn, 2>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, a, b, out, g, LibmSplit{});
     return cudaGetLastError();
 }
 
@@ -892,7 +905,7 @@ template <class Fn> cudaError_t run_binary(const float *a, const float *b, float
     if constexpr (Fn::TAIL) {
         if (e == cudaSuccess && (p.n & 7)) {  // ordered behind the body on the same stream: overwrites its last few elements
             auto g = make_gather_plan<2>(p);
-            B200_LAUNCH((binary_tail_kernel<Fn>), 1, 32, 0, s, a, b, out, g, p.n - (p.n & 7));
+            B200_LAUNCH_ORDERED((binary_tail_kernel<Fn>), 1, 32, 0, s, a, b, out, g, p.n - (p.n & 7));
             e = cudaGetLastError();
         }
     }
@@ -907,7 +920,7 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
     split.mode = ist == 1 ? 0 : ist == 0 ? 1 : 2;
     if (p.nd <= 1 && (p.nd == 0 || p.dim[0].stride[0] == 1)) {
         const uint64_t n_poly = p.nd == 0 ? 0 : p.n - (p.n & 7);
-        B200_LAUNCH((unary_flat_kernel<Fn>), tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, x, out, p.n, n_poly);
+        B200_LAUNCH_ORDERED((unary_flat_kernel<Fn>), tiles_for((p.n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, x, out, p.n, n_poly);
         return cudaGetLastError();
     }
     if (p.nd >= 2 && inner_is_unit_or_zero<1>(p)) {
@@ -917,12 +930,12 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         const unsigned grid = tiles_for(items, EW_BLOCK * EW_UNROLL);
         if (rows_plan_fits_32bit(items, p.dim[p.nd - 1].size)) {
             auto plan = make_rows_plan<uint32_t, 1>(p, vec);
-            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
-            else B200_LAUNCH((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            if (vec == 4) B200_LAUNCH_ORDERED((unary_rows_kernel<Fn, uint32_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            else B200_LAUNCH_ORDERED((unary_rows_kernel<Fn, uint32_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
         } else {
             auto plan = make_rows_plan<uint64_t, 1>(p, vec);
-            if (vec == 4) B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
-            else B200_LAUNCH((unary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            if (vec == 4) B200_LAUNCH_ORDERED((unary_rows_kernel<Fn, uint64_t, 4>), grid, EW_BLOCK, 0, s, x, out, plan, split);
+            else B200_LAUNCH_ORDERED((unary_rows_kernel<Fn, uint64_t, 1>), grid, EW_BLOCK, 0, s, x, out, plan, split);
         }
         return cudaGetLastError();
     }
@@ -930,18 +943,18 @@ template <class Fn> cudaError_t run_unary(const float *x, float *out, const EwPr
         WideTilePlan<1> w{};
         dim3 wgrid;
         if (make_wide_tile_plan<1>(p, w, wgrid)) {
-            B200_LAUNCH((wide_tile_kernel<Fn, 1>), wgrid, 256, 0, s, x, nullptr, out, w, split);
+            B200_LAUNCH_ORDERED((wide_tile_kernel<Fn, 1>), wgrid, 256, 0, s, x, nullptr, out, w, split);
             return cudaGetLastError();
         }
         TilePlan<1> t{};
         uint64_t ctas = 0;
         if (make_tile_plan<1>(p, t, ctas)) {
-            B200_LAUNCH((tile_kernel<Fn, 1>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, x, nullptr, out, t, split);
+            B200_LAUNCH_ORDERED((tile_kernel<Fn, 1>), (unsigned)ctas, dim3(TILE, TILE_ROWS), 0, s, x, nullptr, out, t, split);
             return cudaGetLastError();
         }
     }
     auto g = make_gather_plan<1>(p);
-    B200_LAUNCH((gather_kernel<Fn, 1>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, x, nullptr, out, g, split);
+    B200_LAUNCH_ORDERED((gather_kernel<Fn, 1>), tiles_for(p.n, EW_BLOCK), EW_BLOCK, 0, s, x, nullptr, out, g, split);
     return cudaGetLastError();
 }
 
@@ -974,22 +987,22 @@ cudaError_t launch_binary(uint32_t op, const float *a, const float *b, float *ou
 }
 
 cudaError_t launch_axpy(const float *a, const float *b, float *out, float alpha, uint64_t n, cudaStream_t s) {
-    B200_LAUNCH(axpy_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, a, b, out, alpha, n);
+    B200_LAUNCH_ORDERED(axpy_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, a, b, out, alpha, n);
     return cudaGetLastError();
 }
 
 cudaError_t launch_fill(float *out, uint64_t n, float v, cudaStream_t s) {
-    B200_LAUNCH(fill_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, out, n, v);
+    B200_LAUNCH_ORDERED(fill_kernel, tiles_for((n + 3) / 4, EW_BLOCK * EW_UNROLL), EW_BLOCK, 0, s, out, n, v);
     return cudaGetLastError();
 }
 
 cudaError_t launch_randn(float *out, uint64_t n, uint64_t seed, cudaStream_t s) {
-    B200_LAUNCH(randn_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed);
+    B200_LAUNCH_ORDERED(randn_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed);
     return cudaGetLastError();
 }
 
 cudaError_t launch_rand_uniform(float *out, uint64_t n, uint64_t seed, float lo, float scale, uint64_t first, cudaStream_t s) {
-    B200_LAUNCH(rand_uniform_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed, lo, scale, first);
+    B200_LAUNCH_ORDERED(rand_uniform_kernel, tiles_for((n + 3) / 4, EW_BLOCK), EW_BLOCK, 0, s, out, n, seed, lo, scale, first);
     return cudaGetLastError();
 }
 
@@ -997,7 +1010,7 @@ cudaError_t launch_matmul(const float *a, uint64_t ars, uint64_t acs, const floa
                           uint64_t m, uint64_t n, uint64_t k, cudaStream_t s) {
     const uint64_t tiles_n = (n + TILE - 1) / TILE, tiles_m = (m + TILE - 1) / TILE;
     if (tiles_n * tiles_m > 0x7fffffffull) return cudaErrorInvalidValue;  // an output of more than 2^41 elements
-    B200_LAUNCH(matmul_kernel, (unsigned)(tiles_n * tiles_m), dim3(TILE, TILE), 0, s, a, ars, acs, b, brs, bcs, c, m, n, k, (uint32_t)tiles_n);
+    B200_LAUNCH_ORDERED(matmul_kernel, (unsigned)(tiles_n * tiles_m), dim3(TILE, TILE), 0, s, a, ars, acs, b, brs, bcs, c, m, n, k, (uint32_t)tiles_n);
     return cudaGetLastError();
 }
 

@@ -66,6 +66,7 @@ __device__ __forceinline__ float warp_block_sum(const float *__restrict__ p, uin
 // row the row's result is written directly as 0.0 + block sum (the reference's combine loop).
 __global__ void __launch_bounds__(32 * SUM_WARPS) sum_rows_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len,
                                                                   uint64_t blocks, float *__restrict__ dst) {
+    ordered_start();
     const uint64_t t = (uint64_t)blockIdx.x * SUM_WARPS + (threadIdx.x >> 5);
     if (t >= tasks) return;
     const int lane = threadIdx.x & 31;
@@ -258,6 +259,7 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
 // The cross-GPU step alone, for reductions whose local part did not end in a combiner CTA (short
 // inputs): reads this GPU's finished result from the output locations and overwrites them.
 __global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant__ PeerXchg px, int kind, float *v, int64_t *i, int *status) {
+    ordered_start();
     peer_finish(px, kind, v ? v[0] : 0.0f, i ? i[0] : (int64_t)px.rank, v, i, status);  // no position: the rank breaks ties
 }
 
@@ -275,6 +277,7 @@ constexpr size_t PEER_VECTOR_AREA_WORD = 512;        // first word of the vector
 
 __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_constant__ PeerXchg px, const float *__restrict__ partial, uint32_t m,
                                                               float *__restrict__ out, int *status) {
+    ordered_start();
     const uint32_t j = blockIdx.x * 256 + threadIdx.x;
     bool ok = true;
     if (j < m) {
@@ -370,13 +373,17 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
 template <bool FUSED, int STAGES, uint32_t CHUNK>
 __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
                                                           float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch,
-                                                          const __grid_constant__ PeerXchg px) {
+                                                          const __grid_constant__ PeerXchg px, uint32_t ordered) {
     constexpr uint32_t CHUNK_BYTES = CHUNK * 4;
     extern __shared__ __align__(128) unsigned char tma_smem[];
     __shared__ uint64_t bars[STAGES];
     float *ring = reinterpret_cast<float *>(tma_smem);
     if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status, px);
-    if (FUSED) launch_dependents();  // a worker needs nothing from the kernel before and holds nothing the next one wants
+    // `ordered`: what came before in the stream may have written this kernel's input, so it waits for
+    // that to complete like every other kernel. Otherwise (the kernel before is a reduction of other
+    // buffers) a worker needs nothing from it and starts streaming at once.
+    if (!FUSED || ordered) ordered_start();
+    else launch_dependents();
     const uint64_t t = FUSED ? blockIdx.x - 1 : blockIdx.x;
     const int lane = threadIdx.x;
     if (lane == 0) {
@@ -444,6 +451,7 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
 // Rows shorter than 32 elements never fill a slot: the reference adds them one by one to 0.0.
 __global__ void __launch_bounds__(256) sum_short_rows_kernel(const float *__restrict__ x, uint64_t outer, uint32_t len,
                                                              float *__restrict__ out) {
+    ordered_start();
     const uint64_t r = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (r >= outer) return;
     const float *p = x + r * len;
@@ -460,6 +468,7 @@ constexpr int COMBINE_THREADS = 256;
 constexpr int COMBINE_STAGE = 4096;
 __global__ void __launch_bounds__(COMBINE_THREADS) sum_combine_kernel(const float *__restrict__ partial, uint64_t blocks,
                                                                       float *__restrict__ out) {
+    ordered_start();
     __shared__ float stage[COMBINE_STAGE + 32];
     const uint64_t row = blockIdx.x;
     const float *p = partial + row * blocks;
@@ -499,6 +508,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) sum_combine_kernel(const floa
 constexpr int COL_UNROLL = 8;
 __global__ void __launch_bounds__(256) sum_cols_kernel(const float *__restrict__ x, uint64_t total, uint64_t len, uint64_t inner,
                                                        float *__restrict__ out) {
+    ordered_start();
     const uint64_t t = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (t >= total) return;
     const uint64_t o = t / inner, i = t - o * inner;
@@ -539,6 +549,7 @@ __device__ __forceinline__ void tile_load_2d(void *dst, const CUtensorMap *map, 
 template <int COLS_TILE_ROWS>
 __global__ void __launch_bounds__(32) sum_cols_tma_kernel(const __grid_constant__ CUtensorMap map, uint64_t len, uint64_t inner,
                                                           uint32_t groups_per_outer, float *__restrict__ out, int *status) {
+    ordered_start();
     constexpr uint32_t COLS_TILE_BYTES = COLS_TILE_ROWS * 32 * sizeof(float);
     extern __shared__ __align__(128) unsigned char cols_ring[];
     __shared__ uint64_t bars[COLS_STAGES];
@@ -638,6 +649,7 @@ __device__ __forceinline__ float4 ldmatrix_rows4(uint32_t addr) {
 template <int STAGES, int LDM_ROWS>
 __global__ void __launch_bounds__(64) sum_cols_ldm_kernel(const __grid_constant__ CUtensorMap map, uint64_t len, uint64_t inner,
                                                           uint32_t groups_per_outer, float *__restrict__ out, int *status) {
+    ordered_start();
     constexpr uint32_t LDM_TILE_BYTES = LDM_ROWS * 32 * sizeof(float);
     extern __shared__ unsigned char ldm_raw[];
     const uint32_t base = (smem_addr(ldm_raw) + 127u) & ~127u;
@@ -854,6 +866,7 @@ struct MaxFused {
     int64_t final_offset;
     int *status;
     PeerXchg px;
+    int ordered;  // workers wait for the kernel before this one to complete before they read (see sum_rows_tma_kernel)
 };
 
 // inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
@@ -867,7 +880,8 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
     constexpr int PER_CTA = MAX_CTA / TPT;
     if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
         return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px);
-    if (TPT == MAX_CTA && fused.mailbox != nullptr) launch_dependents();
+    if (TPT == MAX_CTA && fused.mailbox != nullptr && !fused.ordered) launch_dependents();
+    else ordered_start();
     const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
     const uint64_t t = cta * PER_CTA + threadIdx.x / TPT;
     const int lane = threadIdx.x % TPT;
@@ -956,6 +970,7 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
 __global__ void __launch_bounds__(256) max_combine_kernel(const float *__restrict__ pv, const int64_t *__restrict__ pi, uint64_t outer,
                                                           uint64_t segs, float *__restrict__ out_v, int64_t *__restrict__ out_i,
                                                           int64_t idx_offset) {
+    ordered_start();
     __shared__ float sv[8];
     __shared__ uint64_t ss[8];
     const uint64_t r = blockIdx.x;
@@ -989,6 +1004,7 @@ __global__ void __launch_bounds__(256) max_combine_kernel(const float *__restric
 // inner > 1: thread per output column scans rows j in order.
 __global__ void __launch_bounds__(256) max_cols_kernel(const float *__restrict__ x, uint64_t total, uint64_t len, uint64_t inner,
                                                        float *__restrict__ out_v, int64_t *__restrict__ out_i, int64_t idx_offset) {
+    ordered_start();
     const uint64_t t = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (t >= total) return;
     const uint64_t o = t / inner, i = t - o * inner;
@@ -1012,6 +1028,7 @@ __global__ void __launch_bounds__(256) max_cols_kernel(const float *__restrict__
 // best candidate's position is kept (NaN wins, then the larger value, then the lower position).
 __global__ void __launch_bounds__(256) argmax_combine_kernel(const float *__restrict__ vals, const int64_t *__restrict__ idx, uint64_t g,
                                                              uint64_t m, int64_t *__restrict__ out) {
+    ordered_start();
     const uint64_t j = (uint64_t)blockIdx.x * 256 + threadIdx.x;
     if (j >= m) return;
     float bv = vals[j];
@@ -1119,7 +1136,10 @@ unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
     return box[device] + (size_t)(next[device] % MAILBOX_REGIONS) * MAILBOX_SLOTS * 2;
 }
 
-// PYTORCHES_B200_OVERLAP=0 turns the early start of back-to-back reductions off (diagnostic, read once).
+}  // namespace
+
+// PYTORCHES_B200_OVERLAP=0 turns early scheduling and the early start of back-to-back reductions off
+// (every kernel is then launched the ordinary way; diagnostic, read once).
 bool overlap_enabled() {
     static const bool enabled = [] {
         const char *e = getenv("PYTORCHES_B200_OVERLAP");
@@ -1128,6 +1148,7 @@ bool overlap_enabled() {
     return enabled;
 }
 
+namespace {
 // The staged row sum's ring shapes (stages, floats per copy). pick_ring chooses by the number of
 // worker CTAs: see the comment at TMA_MIN_CHUNK. PYTORCHES_B200_SUM_RING=<index> forces one (diagnostic).
 struct RingShape { int stages; uint32_t chunk; };
@@ -1341,7 +1362,7 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         if (len == 0) return launch_fill(o, total, 0.0f, s);  // reduce.rs:106-109
         if (inner == 1) {
             if (len < 32) {
-                B200_LAUNCH(sum_short_rows_kernel, (unsigned)((outer + 255) / 256), 256, 0, s, x, outer, (uint32_t)len, o);
+                B200_LAUNCH_ORDERED(sum_short_rows_kernel, (unsigned)((outer + 255) / 256), 256, 0, s, x, outer, (uint32_t)len, o);
                 return cudaGetLastError();
             }
             const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK, tasks = outer * blocks;
@@ -1357,13 +1378,13 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
 #define B200_RING_CASE(I)                                                                                                                   \
     if (ring == I) {                                                                                                                        \
         if (mailbox)                                                                                                                        \
-            B200_LAUNCH_OVERLAP(early, (sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + 1, 32,               \
+            B200_LAUNCH_ORDERED((sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + 1, 32,                      \
                                 ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, o, status, mailbox, epoch,           \
-                                px ? *px : no_peers);                                                                                       \
+                                px ? *px : no_peers, early ? 0u : 1u);                                                                      \
         else                                                                                                                                \
-            B200_LAUNCH((sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks, 32,                                 \
-                        ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, dst, status, (unsigned long long *)nullptr,  \
-                        0u, no_peers);                                                                                                      \
+            B200_LAUNCH_ORDERED((sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks, 32,                         \
+                                ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, dst, status,                         \
+                                (unsigned long long *)nullptr, 0u, no_peers, 1u);                                                           \
     }
                 B200_RING_CASE(0) B200_RING_CASE(1) B200_RING_CASE(2) B200_RING_CASE(3) B200_RING_CASE(4)
 #undef B200_RING_CASE
@@ -1373,9 +1394,9 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
                     return cudaGetLastError();
                 }
             } else {
-                B200_LAUNCH(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
+                B200_LAUNCH_ORDERED(sum_rows_kernel, (unsigned)((tasks + SUM_WARPS - 1) / SUM_WARPS), 32 * SUM_WARPS, 0, s, x, tasks, len, blocks, dst);
             }
-            if (blocks > 1) B200_LAUNCH(sum_combine_kernel, (unsigned)outer, COMBINE_THREADS, 0, s, (const float *)scratch, blocks, o);
+            if (blocks > 1) B200_LAUNCH_ORDERED(sum_combine_kernel, (unsigned)outer, COMBINE_THREADS, 0, s, (const float *)scratch, blocks, o);
             return cudaGetLastError();
         }
         // Few, long columns: the TMA-staged kernel takes the loading off the ordered chains. Many
@@ -1397,19 +1418,19 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
             const bool tall_tiles = ctas <= (unsigned)sm_count(device) && len >= 1024;
             if (matrix_loads && status && make_cols_tensor_map(&map, x, outer * len, inner, tall_tiles ? 256 : 128)) {
                 if (tall_tiles)
-                    B200_LAUNCH((sum_cols_ldm_kernel<4, 256>), ctas, 64, ldm_smem(4, 256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                    B200_LAUNCH_ORDERED((sum_cols_ldm_kernel<4, 256>), ctas, 64, ldm_smem(4, 256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
                 else
-                    B200_LAUNCH((sum_cols_ldm_kernel<4, 128>), ctas, 64, ldm_smem(4, 128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                    B200_LAUNCH_ORDERED((sum_cols_ldm_kernel<4, 128>), ctas, 64, ldm_smem(4, 128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
                 return cudaGetLastError();
             }
             const bool tall = ctas < 2u * (unsigned)sm_count(device) && len >= 1024;
             if (status && make_cols_tensor_map(&map, x, outer * len, inner, tall ? 256 : 128)) {
-                if (tall) B200_LAUNCH(sum_cols_tma_kernel<256>, ctas, 32, cols_smem(256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
-                else B200_LAUNCH(sum_cols_tma_kernel<128>, ctas, 32, cols_smem(128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                if (tall) B200_LAUNCH_ORDERED(sum_cols_tma_kernel<256>, ctas, 32, cols_smem(256), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
+                else B200_LAUNCH_ORDERED(sum_cols_tma_kernel<128>, ctas, 32, cols_smem(128), s, map, len, inner, (uint32_t)groups_per_outer, o, status);
                 return cudaGetLastError();
             }
         }
-        B200_LAUNCH(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
+        B200_LAUNCH_ORDERED(sum_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, o);
         return cudaGetLastError();
     }
     // MAX writes values, ARGMAX positions, MAX_ARGMAX both.
@@ -1417,7 +1438,7 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     float *ov = kind == REDUCE_ARGMAX ? nullptr : out_v;
     int64_t *oi = arg ? out_i : nullptr;
     if (inner != 1) {
-        B200_LAUNCH(max_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi, idx_offset);
+        B200_LAUNCH_ORDERED(max_cols_kernel, (unsigned)((total + 255) / 256), 256, 0, s, x, total, len, inner, ov, oi, idx_offset);
         return cudaGetLastError();
     }
     MaxPlan m = plan_max(outer, len, sm_count(device));
@@ -1434,10 +1455,10 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         uint32_t epoch = 0;
         unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
         if (mailbox) {
-            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers};
+            early = may_overlap(prev, x, len, ov, oi);
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers, early ? 0 : 1};
             grid += 1;
             *peer_done = px != nullptr;
-            early = may_overlap(prev, x, len, ov, oi);
         }
     }
     if (!fused.mailbox && !ov && spare_v) ov = spare_v;  // the maximum must rest somewhere until the exchange launch reads it
@@ -1452,8 +1473,8 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     if (fused.mailbox) pi = arg ? (int64_t *)(fused.mailbox + MAILBOX_SLOTS) : nullptr;
 #define B200_MAX_CASE(TPT, VEC)                                                                                                                        \
     if (m.tpt == TPT && m.vec == VEC) {                                                                                                                \
-        if (arg) B200_LAUNCH_OVERLAP(early, (max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);  \
-        else B200_LAUNCH_OVERLAP(early, (max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);     \
+        if (arg) B200_LAUNCH_ORDERED((max_rows_kernel<TPT, VEC, true>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);  \
+        else B200_LAUNCH_ORDERED((max_rows_kernel<TPT, VEC, false>), grid, MAX_CTA, 0, s, x, tasks, len, m.segs, m.seg_len, pv, pi, off1, fused);     \
     }
     B200_MAX_CASE(32, 1)
     B200_MAX_CASE(32, 4)
@@ -1461,7 +1482,7 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
     if (fused.mailbox) chain_opened(next, x, len, ov, oi);
-    if (m.segs > 1 && !fused.mailbox) B200_LAUNCH(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
+    if (m.segs > 1 && !fused.mailbox) B200_LAUNCH_ORDERED(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
     return cudaGetLastError();
 }
 }  // namespace
@@ -1488,7 +1509,7 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
     if (position_only) out_v = spare_v;  // where the local pass left this GPU's maximum
     int *status = reduce_status_word(device);
     if (!status) return cudaErrorMemoryAllocation;
-    B200_LAUNCH(peer_exchange_kernel, 1, 32, 0, s, *px, (int)kind, out_v, kind == REDUCE_MAX_ARGMAX ? out_i : (int64_t *)nullptr, status);
+    B200_LAUNCH_ORDERED(peer_exchange_kernel, 1, 32, 0, s, *px, (int)kind, out_v, kind == REDUCE_MAX_ARGMAX ? out_i : (int64_t *)nullptr, status);
     return cudaGetLastError();
 }
 
@@ -1496,14 +1517,14 @@ cudaError_t launch_peer_vector_sum(const PeerXchg &px, const float *partial, uin
     if (px.world <= 0 || m == 0 || m > PEER_VECTOR_MAX) return cudaErrorInvalidValue;
     int *status = reduce_status_word(device);
     if (!status) return cudaErrorMemoryAllocation;
-    B200_LAUNCH(peer_vector_sum_kernel, (unsigned)((m + 255) / 256), 256, 0, s, px, partial, (uint32_t)m, out, status);
+    B200_LAUNCH_ORDERED(peer_vector_sum_kernel, (unsigned)((m + 255) / 256), 256, 0, s, px, partial, (uint32_t)m, out, status);
     return cudaGetLastError();
 }
 
 uint64_t peer_vector_max() { return PEER_VECTOR_MAX; }
 
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s) {
-    B200_LAUNCH(argmax_combine_kernel, (unsigned)((m + 255) / 256), 256, 0, s, vals, idx, g, m, out);
+    B200_LAUNCH_ORDERED(argmax_combine_kernel, (unsigned)((m + 255) / 256), 256, 0, s, vals, idx, g, m, out);
     return cudaGetLastError();
 }
 

@@ -48,6 +48,38 @@ def test_single_rank_group_column_sums_through_the_window(b200, rows, cols):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("n", [70_001, (1 << 22) + 3])
+def test_pointers_inside_a_buffer_take_the_narrow_load_kernels(b200, n):
+    """The extension entry points accept any 4-byte aligned f32 pointer, not only the start of a plugin
+    buffer. A pointer that is not 16-byte aligned must not reach the bulk-copy or 128-bit-load kernels
+    (a misaligned access would be a device fault, not a status): it takes the narrow-load forms, whose
+    results carry the same bits. A pointer that is not even 4-byte aligned is refused."""
+    import ctypes as C
+
+    lib = b200.lib
+    reduce_ = lib.pytorches_b200_peer_reduce
+    reduce_.restype, reduce_.argtypes = C.c_int32, [C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int64, C.c_uint64, C.c_void_p]
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange(), b200.last_error()
+    x = (np.round(lcg_data(n + 3, 11) * 64) / 64).astype(np.float32)
+    whole = Tensor.from_numpy(x, dev)
+    for shift in (1, 2, 3):  # elements: 4, 8, 12 bytes into the buffer
+        view = Tensor.from_numpy(x[shift:shift + n], dev)  # the same values at an aligned address
+        want = [view.sum().numpy(), view.max().numpy(), view.argmax().numpy()]
+        for kind, w in zip((0, 1, 2), want):
+            out = Tensor.zeros_on([2], dev)
+            assert reduce_(0, kind, whole.buffer.ptr + 4 * shift, n, 0, 1000 + shift * 3 + kind, out.buffer.ptr) == abi.STATUS_OK, b200.last_error()
+            got = out.numpy()
+            if kind == 2:
+                assert int(got.view(np.int64)[0]) == int(w)
+            else:
+                assert got.view(np.uint32)[0] == np.float32(w).reshape(1).view(np.uint32)[0], (kind, shift, got[0], w)
+    out = Tensor.zeros_on([2], dev)
+    assert reduce_(0, 0, whole.buffer.ptr + 2, n, 0, 2000, out.buffer.ptr) == abi.STATUS_INVALID_ARGUMENT
+    b200.synchronize(0)
+
+
 def test_column_sums_wider_than_the_window_are_refused(b200):
     import ctypes as C
 
