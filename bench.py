@@ -200,15 +200,28 @@ def check_against_host(res, parts: list[dict]) -> None:
     assert int(res[3]) == where, ("argmax", int(res[3]), where)
 
 
-def oracle_shard_sum(shard: np.ndarray):
-    """The CPU oracle's SUM_AXIS of this rank's shard (None if the oracle has not been built). Checker only."""
+def oracle_shard_sums(shard: np.ndarray):
+    """From the CPU oracle (None if it has not been built; checker only): its SUM_AXIS of this rank's
+    shard, and its sums of the shard's 65536-element blocks (the units the reference chains in block
+    order, plugins/cpu/src/reduce.rs:110-131)."""
     if not os.path.exists(ORACLE_SO):
         return None
     from pytorches_b200.abi import Plugin
     from pytorches_b200.core import Device, Tensor
 
     dev = Device(Plugin(ORACLE_SO), 0)
-    return Tensor.from_numpy(shard, dev).sum().numpy().reshape(())
+    t = Tensor.from_numpy(shard, dev)
+    whole = float(t.sum().numpy().reshape(()))
+    blocks = t.raw_reshape([shard.size // 65536, 65536]).raw_sum_axis(1).numpy() if shard.size % 65536 == 0 else None
+    return whole, blocks
+
+
+def chain_f32(values) -> np.float32:
+    """((0 + v0) + v1) + ... in f32, the reference's combine of block sums."""
+    acc = np.float32(0.0)
+    for v in values:
+        acc = np.float32(acc + np.float32(v))
+    return acc
 
 
 def main():
@@ -289,7 +302,9 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
         """One step; ``pick(j)`` is the tensor op j reads (the same values in every copy)."""
         if world == 1:
             return [pick(0).sum(), pick(1).mean(), pick(2).max(), pick(3).argmax()]
-        return [group.sum(pick(0)), group.mean(pick(1), N_ELEMS), group.max(pick(2)), group.argmax(pick(3), first)]
+        # With the in-kernel exchange on, sum and mean are taken in UNSPLIT order (the shards are whole
+        # 65536-element blocks): the bits of the one-GPU result at every N.
+        return [group.sum(pick(0), first, N_ELEMS), group.mean(pick(1), N_ELEMS, first), group.max(pick(2)), group.argmax(pick(3), first)]
 
     rotating = lambda j: xs[j % copies]
 
@@ -309,42 +324,60 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
     # ---- correctness gate before any timing, at every N: the device's results for the whole tensor against
     # (a) numpy in f64 on the host shards and (b) the CPU oracle's per-shard sums combined in rank order ----
     parts = gather(host_reference(host_np, first))
-    res = [r.numpy() for r in step(rotating)]
+    res = [r.numpy() for r in step(rotating)]  # N > 1: through NCCL, per-rank results combined in rank order
     check_against_host(res, parts)
     checks = {"vs_host_f64": True}
-    mine = oracle_shard_sum(host_np)
-    shard_sums = gather(None if mine is None else float(mine))
-    if all(s is not None for s in shard_sums):
+    mine = oracle_shard_sums(host_np)
+    every = gather(mine)
+    want_unsplit = None
+    if all(m is not None for m in every):
         if world == 1:
-            want = np.float32(shard_sums[0])
+            want = np.float32(every[0][0])
         else:  # SUM_AXIS over the [world] tensor of per-rank sums: added one by one to 0.0, then 0.0 + that
-            acc = np.float32(0.0)
-            for s in shard_sums:
-                acc = np.float32(acc + np.float32(s))
-            want = np.float32(np.float32(0.0) + acc)
+            want = np.float32(np.float32(0.0) + chain_f32(m[0] for m in every))
         assert np.float32(res[0]).tobytes() == want.tobytes(), ("sum differs from the oracle's rank-ordered combine", float(res[0]), float(want))
         assert np.float32(res[1]).tobytes() == np.float32(want / np.float32(N_ELEMS)).tobytes(), "mean differs from the oracle's"
         checks["sum_mean_bit_equal_to_oracle_rank_ordered"] = True
+        if all(m[1] is not None for m in every):  # the oracle's sum over the UNSPLIT tensor: all block sums chained in block order
+            want_unsplit = chain_f32(np.concatenate([m[1] for m in every]))
+            if world == 1:
+                assert want_unsplit.tobytes() == want.tobytes(), "the chain of the oracle's block sums is not the oracle's sum"
 
     # ---- N > 1: move the exchange into the reduction kernels (peer stores over NVLink, one launch per
-    # reduction, no collective library on the data path) if it sets up on every rank AND reproduces the
-    # NCCL path's results bit for bit here; otherwise stay on NCCL. PYTORCHES_B200_PEER_EXCHANGE=0 keeps NCCL. ----
+    # reduction, no collective library on the data path) if it sets up on every rank AND passes its checks
+    # here: max and argmax bit-equal to the NCCL path's, sum and mean (now in unsplit order) bit-equal to
+    # the oracle's over the unsplit tensor and within tolerance of numpy; otherwise stay on NCCL.
+    # PYTORCHES_B200_PEER_EXCHANGE=0 keeps NCCL. ----
     if world > 1 and os.environ.get("PYTORCHES_B200_PEER_EXCHANGE", "1") != "0":
         ok = group.enable_peer_exchange()
+        again = None
         if ok:
             try:
                 again = [r.numpy() for r in step(rotating)]
-                ok = all(a.tobytes() == b.tobytes() for a, b in zip(again, res))
-            except Exception as e:  # a bounded wait ran out, or the call failed: the device stays usable
-                print(f"rank {rank}: in-kernel exchange failed its check: {e}", file=sys.stderr)
+                check_against_host(again, parts)
+                ok = again[2].tobytes() == res[2].tobytes() and again[3].tobytes() == res[3].tobytes()
+                if ok and group.unsplit_order(N_ELEMS) and want_unsplit is not None:
+                    ok = (np.float32(again[0]).tobytes() == want_unsplit.tobytes()
+                          and np.float32(again[1]).tobytes() == np.float32(want_unsplit / np.float32(N_ELEMS)).tobytes())
+                elif ok:
+                    ok = again[0].tobytes() == res[0].tobytes() and again[1].tobytes() == res[1].tobytes()
+            except Exception as e:  # a bounded wait ran out, a check failed, or the call failed: the device stays usable
+                print(f"rank {rank}: in-kernel exchange failed its check: {e!r}", file=sys.stderr)
                 ok = False
             ok = all(gather(ok))
         if ok:
             exchange = "inside the reduction kernels: peer stores into every rank's window, ordered combine in the same launch"
-            checks["vs_nccl_path_bit_equal"] = True
+            checks["max_argmax_bit_equal_to_nccl_path"] = True
+            if group.unsplit_order(N_ELEMS):
+                exchange += "; sum and mean in unsplit order (every rank chains all 4096 block sums)"
+                if want_unsplit is not None:
+                    checks["sum_mean_bit_equal_to_oracle_unsplit"] = True
+            res = again  # what the timed steps must reproduce
         else:
             group.disable_peer_exchange()
             print(f"rank {rank}: staying on the NCCL exchange", file=sys.stderr)
+    elif world == 1 and want_unsplit is not None:
+        checks["sum_mean_bit_equal_to_oracle_unsplit"] = True
 
     def record_step():
         """Runs one step for real through the recorder; returns (its call list, its results)."""
@@ -407,6 +440,16 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
                 host_ms = (time.perf_counter() - t_host) * 1e3 / total  # time the host needs to ENQUEUE one step
                 barrier()
             l1 = launches()
+            trace = None
+            if world > 1 and group.peer_exchange and os.environ.get("PYTORCHES_B200_PEER_TRACE") == "1":  # where the sharded reductions' time went, by the device's clock
+                rec_t, last = group.peer_trace().astype(np.int64), group.peer_seq
+                trace = {}
+                for j, name in enumerate(OPS):  # reduction number q is op q % 4 of a step; its record is (q % 0xfffffffe + 1) % 64
+                    rows = [rec_t[(q % 0xfffffffe + 1) % 64] for q in range(max(last - 64, 0), last) if q % len(OPS) == j]
+                    rows = [r for r in rows if r[1:].min() > 0 and r[3] >= r[2] >= r[1]]
+                    if rows:
+                        trace[name] = {"wait_for_slowest_peer_us": round(statistics.median((r[2] - r[1]) / 1e3 for r in rows), 2),
+                                       "after_last_arrival_us": round(statistics.median((r[3] - r[2]) / 1e3 for r in rows), 2)}
             # after the timed region: one more step, read back, must still be the gate's values
             same = all(a.numpy().tobytes() == b.tobytes() for a, b in zip(step(rotating), res))
             if not same:
@@ -414,7 +457,7 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
             ms_total = ev[0].elapsed_time(ev[-1])
             per_group = [ev[g].elapsed_time(ev[g + 1]) / sizes[g] for g in range(groups)]
             return {"ms": ms_total, "passes": total, "inner": inner, "launches": int(l1 - l0), "clocks": clocks, "host_ms": host_ms,
-                    "median_ms": statistics.median(per_group), "calls_per_pass": rec.executes if native else None,
+                    "median_ms": statistics.median(per_group), "calls_per_pass": rec.executes if native else None, "trace": trace,
                     "driver": "recorded call list replayed by pytorches_b200_replay" if native else "Python mirror of the core"}
         except pytorches_b200.abi.PluginError as e:
             print(f"rank {rank}: timed region failed: {e}", file=sys.stderr)
@@ -426,12 +469,14 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
         if not all(flags) and group.peer_exchange:  # every rank goes back to NCCL together and measures again
             print(f"rank {rank}: in-kernel exchange failed during the timed region; measuring with NCCL", file=sys.stderr)
             group.disable_peer_exchange()
-            checks.pop("vs_nccl_path_bit_equal", None)
+            checks.pop("max_argmax_bit_equal_to_nccl_path", None)
+            checks.pop("sum_mean_bit_equal_to_oracle_unsplit", None)
             exchange = "NCCL all-gather of the partials, combined by plugin ops (the in-kernel exchange failed in this run)"
             try:
                 dev.synchronize()
             except pytorches_b200.abi.PluginError:
                 pass  # the deferred report of the failed wait, if this rank had not seen it yet
+            res = [r.numpy() for r in step(rotating)]  # the NCCL path's values are the ones to reproduce now
             timed = timed_region()
             flags = gather(timed is not None)
         if not all(flags):
@@ -439,6 +484,7 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
     elif timed is None:
         raise SystemExit("the timed steps failed or did not reproduce the gate's results")
     ms = timed["ms"]
+    traces = gather(timed["trace"]) if world > 1 else None
     t_ms = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
     rank_ms = [ms]
     if world > 1:
@@ -528,6 +574,7 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
         "frac_of_measured_peak": round(value / (peak * world), 4), "frac_of_8TBps": round(value / (8000.0 * world), 4),
         "clocks": timed["clocks"].summary(), "e2e": e2e, "gpu_launches": timed["launches"], "host_enqueue_ms_per_step": round(timed["host_ms"], 5),
         "rank_ms_per_step": [round(v / passes, 5) for v in rank_ms], "rank_local_ms_per_step_no_exchange": local_ms,
+        "exchange_trace_per_rank": traces,
         "roofline": roofline, "cpu_baseline": cpu, "ops_ms": {k: round(v, 5) for k, v in per_op.items()},
         "results": {"sum": float(res[0]), "mean": float(res[1]), "max": float(res[2]), "argmax": int(res[3])},
         "results_check": checks,

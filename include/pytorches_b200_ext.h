@@ -120,6 +120,34 @@ int32_t pytorches_b200_peer_reduce(uint32_t device, uint32_t kind, const float *
 int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, uint64_t n, uint64_t n_total, uint64_t seq, float *out);
 
 /*
+ * The sum (mean != 0: the mean) of the whole tensor with the BITS OF THE UNSPLIT SUM, for shards that
+ * are runs of whole 65536-element blocks of it (first_index a multiple of 65536, and n too unless the
+ * shard ends the tensor). The reference adds a long row as a chain of 65536-element block sums in
+ * block order (plugins/cpu/src/reduce.rs:110-131); here every GPU's block sums travel to every rank's
+ * window (one self-validating word each, plain peer stores as they are produced) and every rank runs
+ * that chain over all of them, so a tensor reduced on 1, 2, 4 or 8 GPUs gives the same bits, those of
+ * the reference on the unsplit tensor, as its rule for split execution asks
+ * (tests/diff/test_placement.py:135-144). n_total is at most 2^30 elements (16384 blocks); `x` must be
+ * 16-byte aligned. Everything else (seq, bounded waits, error reporting) as for peer_reduce. A replayed
+ * PT_B200_CALL_PEER_REDUCE names it with op = 4 (sum) or 5 (mean), ints[0] = first_index, ints[1] = n_total.
+ */
+int32_t pytorches_b200_peer_sum_unsplit(uint32_t device, const float *x, uint64_t n, uint64_t first_index, uint64_t n_total, uint32_t mean,
+                                        uint64_t seq, float *out);
+
+/*
+ * Where the time of the sharded reductions goes (a diagnostic: set PYTORCHES_B200_PEER_TRACE=1 in the
+ * environment before the windows are attached; off by default because the extra stores were measured
+ * to disturb multi-GPU runs). Every reduction with an in-kernel exchange then leaves four device-clock
+ * readings (nanoseconds, %globaltimer) in a per-device buffer, in record
+ * (seq % 0xfffffffe + 1) % 64: [1] this GPU's own part is complete, [2] every rank's part has
+ * arrived, [3] the result is written ([0] is unused).
+ * [2] - [1] is the wait for the slowest peer (skew between the GPUs plus NVLink latency), [3] - [2]
+ * the work left after the last arrival. This call synchronizes the device's stream and copies the 64
+ * records (64 x 4 uint64) to `records_out`. Replaces nothing in the reference.
+ */
+int32_t pytorches_b200_peer_trace(uint32_t device, uint64_t *records_out);
+
+/*
  * The same for a small vector result: the sum over the leading dimension of a [rows_total, cols]
  * tensor whose rows are split over the ranks, e.g. the bias gradient the reference core computes by
  * SUM_AXIS(0) when it reduces a broadcast gradient back to the bias's shape

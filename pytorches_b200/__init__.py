@@ -28,6 +28,10 @@ def load_plugin() -> Plugin:
     """Load the B200 plugin (once per process). Fails loudly when it has not been built."""
     global _PLUGIN
     if _PLUGIN is None:
+        override = os.environ.get("PYTORCHES_B200_PLUGIN")  # a library built elsewhere (no check against the sources beside this package)
+        if override:
+            _PLUGIN = Plugin(override)
+            return _PLUGIN
         path = plugin_path()
         if not os.path.exists(path):
             raise RuntimeError(

@@ -93,11 +93,19 @@ struct PeerXchg {
     uint32_t epoch;          // never 0; the same on every rank for the same reduction
     uint32_t wait_ms;        // how long to wait for the peers before giving up
     float divide_by;         // a sum's combined result is divided by this when it is not 0 (mean = sum / count)
+    // A sum "in unsplit order": the shards are whole 65536-element blocks of one tensor of blocks_total
+    // blocks, this rank's first being block0. Every worker then stores its block sum into EVERY rank's
+    // window and every rank's combiner chains all blocks_total sums in block order: the result has the
+    // bits of the sum over the unsplit tensor. blocks_total == 0: per-rank results combined in rank order.
+    uint32_t block0;
+    uint32_t blocks_total;
+    unsigned long long *trace;  // this device's trace records (see peer_trace in reduce.cu); ordinary device memory, not part of a window
 };
 // Window management (one window per device of this process). `handle` is a 64-byte CUDA IPC handle.
 cudaError_t peer_window_export(int device, void *handle, cudaStream_t s);
 cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const void *handles, uint32_t wait_ms);
 bool peer_window_for(int device, uint64_t seq, PeerXchg *px);
+cudaError_t peer_trace_read(int device, unsigned long long *out, cudaStream_t s);
 
 size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint64_t inner, int device);
 
@@ -128,6 +136,8 @@ cudaError_t launch_reduce(ReduceKind kind, const float *x, uint64_t outer, uint6
 int take_reduce_status(int device);
 // The cross-GPU step for a vector result: every rank's `partial[0..m)` summed in rank order into
 // `out[0..m)` on every rank (m at most peer_vector_max()); see peer_vector_sum_kernel.
+// Most blocks a sum in unsplit order may have (the window's block area holds that many words per generation).
+uint64_t peer_blocks_max();
 cudaError_t launch_peer_vector_sum(const PeerXchg &px, const float *partial, uint64_t m, float *out, int device, cudaStream_t s);
 uint64_t peer_vector_max();
 // Per column of [g, m] candidates (value, position), the position of the best one.

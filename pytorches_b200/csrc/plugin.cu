@@ -616,6 +616,15 @@ PtStatus peer_attach(uint32_t device, uint32_t rank, uint32_t world, const void 
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer window attach (CUDA IPC)", e);
 }
 
+PtStatus peer_trace(uint32_t device, uint64_t *out) {
+    if (!out) B200_INVALID("b200: peer trace: null pointer");
+    B200_ENTER(device);
+    d.chain.tail_open = false;
+    cudaError_t e = peer_trace_read((int)device, (unsigned long long *)out, d.stream);
+    if (e == cudaErrorInvalidValue) B200_INVALID("b200: peer trace: no window on device %u", device);
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer trace", e);
+}
+
 // kind: 0 sum, 1 max, 2 argmax, 3 mean (the sum divided by `count`, the whole tensor's element count as f32).
 PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n, int64_t first_index, uint64_t seq, void *out, float count = 0.0f) {
     if (kind > 3) B200_INVALID("b200: peer reduce: kind %u is not 0 (sum), 1 (max), 2 (argmax) or 3 (mean)", kind);
@@ -641,6 +650,29 @@ PtStatus peer_reduce(uint32_t device, uint32_t kind, const float *x, uint64_t n,
     if (scratch) free_locked(d, scratch);
     if (value) free_locked(d, value);
     return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer reduce", e);
+}
+
+// The sum (or mean) of a tensor split over the ranks in whole 65536-element blocks, with the bits of the
+// sum over the unsplit tensor: every rank chains ALL block sums in block order (see PeerXchg).
+PtStatus peer_sum_unsplit(uint32_t device, const float *x, uint64_t n, uint64_t first_index, uint64_t n_total, uint32_t mean, uint64_t seq, float *out) {
+    constexpr uint64_t BLOCK = 65536;
+    if (!out || !x) B200_INVALID("b200: peer sum in unsplit order: null pointer");
+    if (n == 0 || first_index % BLOCK || first_index + n > n_total || (first_index + n != n_total && n % BLOCK))
+        B200_INVALID("b200: peer sum in unsplit order: the shard [%llu, %llu) of %llu elements is not a run of whole 65536-element blocks",
+                     (unsigned long long)first_index, (unsigned long long)(first_index + n), (unsigned long long)n_total);
+    const uint64_t blocks_total = (n_total + BLOCK - 1) / BLOCK;
+    if (blocks_total > peer_blocks_max())
+        B200_INVALID("b200: peer sum in unsplit order: %llu blocks, the windows hold %llu", (unsigned long long)blocks_total, (unsigned long long)peer_blocks_max());
+    if (((uintptr_t)x & 15) || ((uintptr_t)out & 3)) B200_INVALID("b200: peer sum in unsplit order: x must be 16-byte aligned, out 4-byte aligned");
+    B200_ENTER(device);
+    PeerXchg px;
+    if (!peer_window_for((int)device, seq, &px)) B200_INVALID("b200: peer sum in unsplit order: no peer windows attached on device %u", device);
+    px.divide_by = mean ? (float)n_total : 0.0f;
+    px.block0 = (uint32_t)(first_index / BLOCK);
+    px.blocks_total = (uint32_t)blocks_total;
+    cudaError_t e = launch_reduce(REDUCE_SUM, x, 1, n, 1, out, nullptr, 0, nullptr, (int)device, d.stream, &px, &d.chain);
+    if (e == cudaErrorInvalidValue) B200_INVALID("b200: peer sum in unsplit order: this shard cannot take the one-launch form");
+    return e == cudaSuccess ? PT_STATUS_OK : cuda_fail("peer sum in unsplit order", e);
 }
 
 // Sum over the leading dimension of a [rows, m] tensor whose rows are split over the ranks: the local
@@ -747,7 +779,10 @@ PtStatus replay(uint32_t device, const PtB200Call *calls, uint32_t n_calls, uint
                     resolve(c.out[0], o);
                     uint64_t n;
                     if (!numel(x.shape, x.ndim, n)) n = 0;
-                    st = peer_reduce(device, c.op, (const float *)x.data, n, c.ints[0], seq++, o.data, (float)c.ints[1]);
+                    if (c.op == 4 || c.op == 5)  // sum / mean in unsplit order
+                        st = peer_sum_unsplit(device, (const float *)x.data, n, (uint64_t)c.ints[0], (uint64_t)c.ints[1], c.op == 5, seq++, (float *)o.data);
+                    else
+                        st = peer_reduce(device, c.op, (const float *)x.data, n, c.ints[0], seq++, o.data, (float)c.ints[1]);
                     break;
                 }
             }
@@ -843,6 +878,25 @@ B200_EXPORT int32_t pytorches_b200_peer_mean(uint32_t device, const float *x, ui
         return b200::peer_reduce(device, 3, x, n, 0, seq, out, (float)n_total);
     } catch (...) {
         b200::set_last_error("b200: peer mean raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_trace(uint32_t device, uint64_t *records_out) {
+    try {
+        return b200::peer_trace(device, records_out);
+    } catch (...) {
+        b200::set_last_error("b200: peer trace raised an exception");
+        return PT_STATUS_INTERNAL;
+    }
+}
+
+B200_EXPORT int32_t pytorches_b200_peer_sum_unsplit(uint32_t device, const float *x, uint64_t n, uint64_t first_index, uint64_t n_total, uint32_t mean,
+                                                    uint64_t seq, float *out) {
+    try {
+        return b200::peer_sum_unsplit(device, x, n, first_index, n_total, mean, seq, out);
+    } catch (...) {
+        b200::set_last_error("b200: peer sum in unsplit order raised an exception");
         return PT_STATUS_INTERNAL;
     }
 }

@@ -153,6 +153,12 @@ __device__ __forceinline__ unsigned long long ld_mailbox(const unsigned long lon
     return v;
 }
 
+__device__ __forceinline__ unsigned long long ld_mailbox_sys(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ bool vi_better(float v, uint64_t i, float bv, uint64_t bi);
 
 // ---- the cross-GPU step --------------------------------------------------------------------------------------
@@ -175,6 +181,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+
+__device__ __forceinline__ void peer_trace(const PeerXchg &px, int what);  // leaves a %globaltimer reading in this rank's window (below)
 
 __device__ __forceinline__ bool peer_allgather(const PeerXchg &px, float v, int64_t pos, float &rv, int64_t &rp, int *status) {
     const int lane = threadIdx.x & 31;
@@ -231,7 +239,9 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
     const int lane = threadIdx.x & 31;
     float rv;
     int64_t rp;
+    if (lane == 0) peer_trace(px, 1);
     if (!peer_allgather(px, v, pos, rv, rp, status)) return;
+    if (lane == 0) peer_trace(px, 2);
     if (kind == REDUCE_SUM) {
         float s = 0.0f;
         for (int r = 0; r < px.world; ++r) s = __fadd_rn(s, __shfl_sync(0xffffffffu, rv, r));
@@ -239,7 +249,10 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
         // A mean is the reference's sum followed by a DIV by the element count as an f32 scalar
         // (crates/core/src/lib.rs:662-670): one IEEE division, the same bits as FILL + DIV.
         if (px.divide_by != 0.0f) s = __fdiv_rn(s, px.divide_by);
-        if (lane == 0) out_v[0] = s;
+        if (lane == 0) {
+            out_v[0] = s;
+            peer_trace(px, 3);
+        }
         return;
     }
     float bv = lane < px.world ? rv : __int_as_float(0xff800000);
@@ -253,6 +266,7 @@ __device__ __forceinline__ void peer_finish(const PeerXchg &px, int kind, float 
     if (lane == 0) {
         if (out_v) out_v[0] = bv;
         if (out_i) out_i[0] = (int64_t)bp;
+        peer_trace(px, 3);
     }
 }
 
@@ -274,6 +288,31 @@ __global__ void __launch_bounds__(32) peer_exchange_kernel(const __grid_constant
 // PEER_VECTOR_MAX words, generations used in turn exactly as for scalars. Waits are bounded in time.
 constexpr uint32_t PEER_VECTOR_MAX = 4096;           // elements (16 KiB of f32)
 constexpr size_t PEER_VECTOR_AREA_WORD = 512;        // first word of the vector area (the scalar area ends before it)
+// After the vector area: the block area for sums in unsplit order, PEER_GENERATIONS x PEER_BLOCKS_MAX
+// words, one per 65536-element block of the whole tensor (2^30 elements at most).
+constexpr uint32_t PEER_BLOCKS_MAX = 16384;
+constexpr size_t PEER_BLOCK_AREA_WORD = PEER_VECTOR_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_VECTOR_MAX;
+// Beside the window, in ordinary memory of the device: a trace of its last PEER_TRACE_RECORDS reductions,
+// four words each (record = epoch mod PEER_TRACE_RECORDS), %globaltimer readings: [1] this GPU's own
+// part is complete (its result ready to send, or its last block sum forwarded), [2] every rank's part
+// has arrived here, [3] the result is written; [0] is unused. [2] - [1] is the wait for the slowest
+// peer (skew plus NVLink latency; in unsplit order it also holds this combiner's wait for the kernel
+// before it), [3] - [2] what is left to do after the last arrival. Read back with
+// pytorches_b200_peer_trace. (A reading at the combiner's start was dropped: a store placed right
+// behind griddepcontrol.launch_dependents, even one that never executes, cost 12% of the step at 2
+// GPUs and 40% at 4 with sums in unsplit order.)
+constexpr uint32_t PEER_TRACE_RECORDS = 64;
+
+__device__ __forceinline__ unsigned long long *own_window(const PeerXchg &px) {
+    unsigned long long *mine = px.window[0];
+#pragma unroll
+    for (int r = 1; r < PEER_MAX_RANKS; ++r)
+        if (px.rank == r) mine = px.window[r];
+    return mine;
+}
+__device__ __forceinline__ void peer_trace(const PeerXchg &px, int what) {
+    if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * 4 + what] = global_ns();
+}
 
 __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_constant__ PeerXchg px, const float *__restrict__ partial, uint32_t m,
                                                               float *__restrict__ out, int *status) {
@@ -313,12 +352,14 @@ __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_const
     }
 }
 
-// A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 256 words
-// per round (8 per lane, all in flight together) and re-polls only the ones not yet published.
-constexpr int COMBINER_WORDS = 8;
+// A poll is a round trip to L2 (a microsecond or more under load), so the combiner fetches 512 words
+// per round (16 per lane, all in flight together), issues the NEXT round's loads before it chains the
+// current round's 512 dependent adds (about a microsecond, so the round trip hides behind the chain
+// once the words are there), and re-polls only the words not yet published.
+constexpr int COMBINER_WORDS = 16;
 
 __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
-                                 const PeerXchg &px) {
+                                 const PeerXchg &px, float *stage) {
     const int lane = threadIdx.x;
     // The kernel before this one (if this one was allowed to start early) completes first; only then
     // may the kernel after this one start. So at most two of these kernels are in flight, they finish
@@ -326,14 +367,111 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
     wait_for_prior_grid();
     launch_dependents();
     float s = 0.0f;
-    for (uint64_t base = 0; base < blocks; base += 32 * COMBINER_WORDS) {
+    // In unsplit order the words are this rank's window, written by every rank's workers: loads at
+    // system scope, and the patience of a wait for peers (time, not tries).
+    const bool unsplit = px.blocks_total != 0;
+    const unsigned long long t0 = unsplit ? global_ns() : 0, limit = (unsigned long long)px.wait_ms * 1000000ull;
+    constexpr uint64_t ROUND = 32 * COMBINER_WORDS;
+    unsigned long long w[COMBINER_WORDS];  // the round whose loads are in flight
+    auto issue = [&](uint64_t base) {
+#pragma unroll
+        for (int k = 0; k < COMBINER_WORDS; ++k)
+            if (base + k * 32 + lane < blocks) w[k] = unsplit ? ld_mailbox_sys(mailbox + base + k * 32 + lane) : ld_mailbox(mailbox + base + k * 32 + lane);
+    };
+    issue(0);
+    for (uint64_t base = 0; base < blocks; base += ROUND) {
         float v[COMBINER_WORDS];
         uint32_t missing = 0;
 #pragma unroll
-        for (int k = 0; k < COMBINER_WORDS; ++k) {
+        for (int k = 0; k < COMBINER_WORDS; ++k) {  // what the loads issued a round ago brought
             v[k] = 0.0f;
-            if (base + k * 32 + lane < blocks) missing |= 1u << k;
+            if (base + k * 32 + lane < blocks) {
+                if ((uint32_t)(w[k] >> 32) == epoch) v[k] = __uint_as_float((uint32_t)w[k]);
+                else missing |= 1u << k;
+            }
         }
+        for (uint32_t tries = 0; (unsplit || tries < POLL_LIMIT) && __any_sync(0xffffffffu, missing != 0); ++tries) {
+            if (unsplit && (tries & 63) == 63 && __any_sync(0xffffffffu, global_ns() - t0 > limit)) break;
+            unsigned long long again[COMBINER_WORDS];
+#pragma unroll
+            for (int k = 0; k < COMBINER_WORDS; ++k)
+                if (missing & (1u << k)) again[k] = unsplit ? ld_mailbox_sys(mailbox + base + k * 32 + lane) : ld_mailbox(mailbox + base + k * 32 + lane);
+#pragma unroll
+            for (int k = 0; k < COMBINER_WORDS; ++k)
+                if ((missing & (1u << k)) && (uint32_t)(again[k] >> 32) == epoch) {
+                    v[k] = __uint_as_float((uint32_t)again[k]);
+                    missing &= ~(1u << k);
+                }
+        }
+        if (__any_sync(0xffffffffu, missing != 0)) {
+            if (lane == 0) {
+                *(volatile int *)status = unsplit ? STATUS_PEER_WAIT_EXPIRED : STATUS_WAIT_EXPIRED;
+                __threadfence_system();
+            }
+            return;
+        }
+        if (base + ROUND < blocks) issue(base + ROUND);  // in flight while this round is chained
+        else if (unsplit && lane == 0) peer_trace(px, 2);  // the last round's words are here: every rank's part has arrived
+        // The round's sums go through shared memory (this CTA's ring is otherwise unused) so that every
+        // lane can run the same chain with 16-byte broadcast loads, four sums per load, the next loads
+        // in flight while the current four adds run: the chain advances at the add latency. (Fetching
+        // each sum from its lane with a shuffle costs five times that, which shows as soon as all
+        // sums are there at once, as they are when a tensor's blocks arrive from several GPUs.)
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < COMBINER_WORDS; ++k) stage[k * 32 + lane] = v[k];
+        __syncwarp();
+        const uint32_t count = (uint32_t)(blocks - base < ROUND ? blocks - base : ROUND);
+        const float4 *quad = reinterpret_cast<const float4 *>(stage);
+        float4 cur[4], nxt[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cur[u] = quad[u];
+        uint32_t i = 0;
+        for (; i + 32 <= count; i += 32) {  // 32 sums per trip: two batches of four float4
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                nxt[u] = quad[i / 4 + 4 + u];
+                s = __fadd_rn(s, cur[u].x);
+                s = __fadd_rn(s, cur[u].y);
+                s = __fadd_rn(s, cur[u].z);
+                s = __fadd_rn(s, cur[u].w);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                cur[u] = quad[(i / 4 + 8 + u) % (ROUND / 4)];  // past the end of the round: wraps to a valid address, the value is dropped
+                s = __fadd_rn(s, nxt[u].x);
+                s = __fadd_rn(s, nxt[u].y);
+                s = __fadd_rn(s, nxt[u].z);
+                s = __fadd_rn(s, nxt[u].w);
+            }
+        }
+        for (; i < count; ++i) s = __fadd_rn(s, stage[i]);
+    }
+    if (unsplit) {  // every rank has chained every block: nothing left to exchange
+        if (px.divide_by != 0.0f) s = __fdiv_rn(s, px.divide_by);
+        if (lane == 0) {
+            out[0] = s;
+            peer_trace(px, 3);
+        }
+        return;
+    }
+    if (px.world > 0) return peer_finish(px, REDUCE_SUM, s, 0, out, nullptr, status);  // s is the same in every lane
+    if (lane == 0) out[0] = s;
+}
+
+// Unsplit order, second special CTA: hands this GPU's block sums to every rank. The workers publish
+// into the local mailbox exactly as they do on one GPU (a store across NVLink at the end of a worker
+// would keep its SM slot busy for the round trip, 1024 times per reduction); this warp polls the local
+// words in rounds and, as they appear, stores each as (group epoch << 32) | bits into the block area of
+// EVERY rank's window, its own included, from where the combiners chain them.
+__device__ void block_forwarder(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, int *status, const PeerXchg &px) {
+    const int lane = threadIdx.x;
+    const size_t at = PEER_BLOCK_AREA_WORD + (size_t)(px.epoch % PEER_GENERATIONS) * PEER_BLOCKS_MAX + px.block0;
+    for (uint64_t base = 0; base < blocks; base += 32 * COMBINER_WORDS) {
+        uint32_t missing = 0;
+#pragma unroll
+        for (int k = 0; k < COMBINER_WORDS; ++k)
+            if (base + k * 32 + lane < blocks) missing |= 1u << k;
         for (uint32_t tries = 0; tries < POLL_LIMIT && __any_sync(0xffffffffu, missing != 0); ++tries) {
             unsigned long long w[COMBINER_WORDS];
 #pragma unroll
@@ -342,8 +480,11 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
 #pragma unroll
             for (int k = 0; k < COMBINER_WORDS; ++k)
                 if ((missing & (1u << k)) && (uint32_t)(w[k] >> 32) == epoch) {
-                    v[k] = __uint_as_float((uint32_t)w[k]);
                     missing &= ~(1u << k);
+                    const unsigned long long out = ((unsigned long long)px.epoch << 32) | (uint32_t)w[k];
+#pragma unroll
+                    for (int r = 0; r < PEER_MAX_RANKS; ++r)
+                        if (r < px.world) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(px.window[r] + at + base + k * 32 + lane), "l"(out) : "memory");
                 }
         }
         if (__any_sync(0xffffffffu, missing != 0)) {
@@ -353,21 +494,8 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
             }
             return;
         }
-        // Every lane runs the same chain; the sums are broadcast by shuffles, which are off the chain.
-#pragma unroll
-        for (int k = 0; k < COMBINER_WORDS; ++k) {
-            const uint64_t first = base + (uint64_t)k * 32;
-            if (first >= blocks) break;
-            if (blocks - first >= 32) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v[k], j));
-            } else {
-                for (int j = 0; j < (int)(blocks - first); ++j) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v[k], j));
-            }
-        }
     }
-    if (px.world > 0) return peer_finish(px, REDUCE_SUM, s, 0, out, nullptr, status);  // s is the same in every lane
-    if (lane == 0) out[0] = s;
+    if (lane == 0) peer_trace(px, 1);
 }
 
 template <bool FUSED, int STAGES, uint32_t CHUNK>
@@ -378,13 +506,22 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
     extern __shared__ __align__(128) unsigned char tma_smem[];
     __shared__ uint64_t bars[STAGES];
     float *ring = reinterpret_cast<float *>(tma_smem);
-    if (FUSED && blockIdx.x == 0) return ordered_combiner(mailbox, epoch, blocks, dst, status, px);
+    if (FUSED && blockIdx.x == 0) {
+        if (px.blocks_total != 0) {  // unsplit order: chain the whole tensor's block sums out of this rank's own window
+            const unsigned long long *mine = own_window(px);
+            return ordered_combiner(mine + PEER_BLOCK_AREA_WORD + (size_t)(px.epoch % PEER_GENERATIONS) * PEER_BLOCKS_MAX, px.epoch, px.blocks_total, dst,
+                                    status, px, ring);
+        }
+        return ordered_combiner(mailbox, epoch, blocks, dst, status, px, ring);
+    }
     // `ordered`: what came before in the stream may have written this kernel's input, so it waits for
     // that to complete like every other kernel. Otherwise (the kernel before is a reduction of other
     // buffers) a worker needs nothing from it and starts streaming at once.
     if (!FUSED || ordered) ordered_start();
     else launch_dependents();
-    const uint64_t t = FUSED ? blockIdx.x - 1 : blockIdx.x;
+    const bool unsplit = FUSED && px.blocks_total != 0;
+    if (unsplit && blockIdx.x == 1) return block_forwarder(mailbox, epoch, blocks, status, px);
+    const uint64_t t = FUSED ? blockIdx.x - (unsplit ? 2 : 1) : blockIdx.x;
     const int lane = threadIdx.x;
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
@@ -1226,10 +1363,11 @@ bool make_cols_tensor_map(CUtensorMap *map, const float *x, uint64_t rows, uint6
 namespace {
 constexpr size_t PEER_WINDOW_BYTES = size_t(2) << 20;
 static_assert(PEER_WINDOW_WORDS <= PEER_VECTOR_AREA_WORD, "the scalar slots end before the vector area");
-static_assert((PEER_VECTOR_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_VECTOR_MAX) * 8 <= PEER_WINDOW_BYTES, "the vector area fits the window");
+static_assert((PEER_BLOCK_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_BLOCKS_MAX) * 8 <= PEER_WINDOW_BYTES, "the vector and block areas fit the window");
 struct PeerWindows {
     std::mutex mu;
     unsigned long long *local[64] = {};
+    unsigned long long *trace[64] = {};  // PEER_TRACE_RECORDS x 4 words per device
     cudaIpcMemHandle_t local_handle[64] = {};
     std::vector<std::pair<cudaIpcMemHandle_t, void *>> opened[64];
     PeerXchg attached[64] = {};
@@ -1254,6 +1392,12 @@ cudaError_t peer_window_export(int device, void *handle, cudaStream_t s) {
         }
         w.local[device] = (unsigned long long *)p;
     }
+    if (!w.trace[device]) {
+        void *t = nullptr;
+        if ((e = cudaMalloc(&t, (size_t)PEER_TRACE_RECORDS * 4 * 8)) != cudaSuccess) return e;
+        w.trace[device] = (unsigned long long *)t;
+    }
+    if ((e = cudaMemsetAsync(w.trace[device], 0, (size_t)PEER_TRACE_RECORDS * 4 * 8, s)) != cudaSuccess) return e;
     w.attached[device] = PeerXchg{};
     // Everything this device has in flight finishes before the window is cleared, and the clearing
     // finishes before the handle leaves this call: no peer can write before it holds the handle.
@@ -1273,6 +1417,13 @@ cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const 
     px.world = (int)world;
     px.rank = (int)rank;
     px.wait_ms = wait_ms ? wait_ms : 2000;
+    // The trace is a diagnostic, off unless PYTORCHES_B200_PEER_TRACE=1: with several GPUs and sums in
+    // unsplit order its few stores per reduction were measured to cost 10-40% of the step.
+    static const bool tracing = [] {
+        const char *e = getenv("PYTORCHES_B200_PEER_TRACE");
+        return e && e[0] == '1';
+    }();
+    px.trace = tracing ? w.trace[device] : nullptr;
     for (uint32_t r = 0; r < world; ++r) {
         cudaIpcMemHandle_t h;
         std::memcpy(&h, (const char *)handles + (size_t)r * sizeof h, sizeof h);
@@ -1293,6 +1444,16 @@ cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const 
     if (px.window[rank] != w.local[device]) return cudaErrorInvalidValue;  // handles[rank] must be this device's own
     w.attached[device] = px;
     return cudaSuccess;
+}
+
+// Copies the trace records of `device`'s own window (PEER_TRACE_RECORDS x 4 words) to the host.
+cudaError_t peer_trace_read(int device, unsigned long long *out, cudaStream_t s) {
+    if (device < 0 || device >= 64 || !out) return cudaErrorInvalidValue;
+    PeerWindows &w = peer_windows();
+    std::lock_guard<std::mutex> lock(w.mu);
+    if (!w.trace[device]) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMemcpyAsync(out, w.trace[device], (size_t)PEER_TRACE_RECORDS * 4 * 8, cudaMemcpyDeviceToHost, s);
+    return e == cudaSuccess ? cudaStreamSynchronize(s) : e;
 }
 
 bool peer_window_for(int device, uint64_t seq, PeerXchg *px) {
@@ -1368,17 +1529,21 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
             const uint64_t blocks = (len + SUM_BLOCK - 1) / SUM_BLOCK, tasks = outer * blocks;
             float *dst = blocks == 1 ? o : (float *)scratch;
             // Long rows whose block starts are 16-byte aligned take the TMA-staged kernel.
-            int *status = (base16 && len >= 8 * TMA_MIN_CHUNK && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word(device) : nullptr;
+            // A sum in unsplit order must take the one-launch form whatever its size: the other ranks wait for its block sums.
+            const bool unsplit = px && px->blocks_total != 0;
+            int *status = (base16 && (unsplit || len >= 8 * TMA_MIN_CHUNK) && (len % 4 == 0 || outer == 1) && tasks <= 0x7fffffffull) ? reduce_status_word(device) : nullptr;
+            if (unsplit && !(status && outer == 1 && blocks <= MAILBOX_SLOTS && staged_kernels_ready(device))) return cudaErrorInvalidValue;
             if (status && staged_kernels_ready(device)) {
                 // A single long row: chain the block sums inside the same launch (see ordered_combiner).
                 uint32_t epoch = 0;
-                unsigned long long *mailbox = (outer == 1 && blocks >= 64 && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
+                unsigned long long *mailbox = (outer == 1 && (blocks >= 64 || unsplit) && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
+                if (unsplit && !mailbox) return cudaErrorInvalidValue;
                 const int ring = pick_ring(tasks, sm_count(device));
                 const bool early = mailbox && may_overlap(prev, x, len, o, nullptr);
 #define B200_RING_CASE(I)                                                                                                                   \
     if (ring == I) {                                                                                                                        \
         if (mailbox)                                                                                                                        \
-            B200_LAUNCH_ORDERED((sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + 1, 32,                      \
+            B200_LAUNCH_ORDERED((sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + (unsplit ? 2 : 1), 32,       \
                                 ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, o, status, mailbox, epoch,           \
                                 px ? *px : no_peers, early ? 0u : 1u);                                                                      \
         else                                                                                                                                \
@@ -1522,6 +1687,7 @@ cudaError_t launch_peer_vector_sum(const PeerXchg &px, const float *partial, uin
 }
 
 uint64_t peer_vector_max() { return PEER_VECTOR_MAX; }
+uint64_t peer_blocks_max() { return PEER_BLOCKS_MAX; }
 
 cudaError_t launch_argmax_combine(const float *vals, const int64_t *idx, uint64_t g, uint64_t m, int64_t *out, cudaStream_t s) {
     B200_LAUNCH_ORDERED(argmax_combine_kernel, (unsigned)((m + 255) / 256), 256, 0, s, vals, idx, g, m, out);

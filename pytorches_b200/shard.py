@@ -118,6 +118,10 @@ class ShardGroup:
             mean_ = lib.pytorches_b200_peer_mean
             mean_.restype, mean_.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
             self._peer_mean = mean_
+            uns_ = lib.pytorches_b200_peer_sum_unsplit
+            uns_.restype = C.c_int32
+            uns_.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_void_p]
+            self._peer_sum_unsplit = uns_
             vec_ = lib.pytorches_b200_peer_sum_axis0
             vec_.restype, vec_.argtypes = C.c_int32, [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
             self._peer_sum_axis0 = vec_
@@ -161,6 +165,16 @@ class ShardGroup:
         note = getattr(dev.plugin, "peer_reduce", None)  # a recorder writes the call down (replay.Recorder)
         if note is not None:
             note(dev.index, kind, x_local.buffer.ptr, x_local.numel(), first_index, n_total, out.buffer.ptr, out.dtype)
+        return out
+
+    def peer_trace(self) -> np.ndarray:
+        """[64, 4] device-clock readings (ns) of this rank's last 64 reductions with an in-kernel exchange,
+        row (seq % 0xfffffffe + 1) % 64: unused, own part complete, every rank's part arrived, result
+        written (``pytorches_b200_peer_trace``; all zero unless PYTORCHES_B200_PEER_TRACE=1). Synchronizes the device's stream."""
+        fn = self.device.plugin.lib.pytorches_b200_peer_trace
+        fn.restype, fn.argtypes = C.c_int32, [C.c_uint32, C.c_void_p]
+        out = np.zeros((64, 4), dtype=np.uint64)
+        self.device.plugin.check(fn(self.device.index, out.ctypes.data), "peer trace")
         return out
 
     def advance_peer_seq(self, to: int) -> None:
@@ -260,14 +274,52 @@ class ShardGroup:
             return out
         return self._defer(lambda: [x_local.raw_sum_axis(0)], x_local.shape[1:], DTYPE_F32, self._combine(op.SUM_AXIS))
 
-    def sum(self, x_local: Tensor) -> Tensor:
-        """Full-tensor sum: every rank's ``Tensor.sum`` partial, combined in rank order."""
+    SUM_BLOCK = 65536        # the reference's summation block (plugins/cpu/src/reduce.rs:10)
+    UNSPLIT_MAX_BLOCKS = 16384
+
+    def unsplit_order(self, n_total: int) -> bool:
+        """Whether a sum over a tensor of ``n_total`` elements, split by ``split_rows`` over this group,
+        can be computed with the bits of the UNSPLIT sum: the in-kernel exchange is on, every shard is a
+        run of whole 65536-element blocks and holds at least one. The same answer on every rank."""
+        import os
+
+        if os.environ.get("PYTORCHES_B200_UNSPLIT_ORDER", "1") == "0":  # diagnostic: keep the rank-ordered combine
+            return False
+        if not self._peer_reduce or n_total <= 0 or -(-n_total // self.SUM_BLOCK) > self.UNSPLIT_MAX_BLOCKS:
+            return False
+        for r in range(self.world):
+            start, count = split_rows(n_total, r, self.world)
+            if count == 0 or start % self.SUM_BLOCK or (start + count != n_total and count % self.SUM_BLOCK):
+                return False
+        return True
+
+    def _peer_unsplit(self, x_local: Tensor, first_index: int, n_total: int, mean: bool) -> Tensor:
+        dev = self.device
+        out = Tensor(Buffer(dev, 1), [])
+        seq, self._peer_seq = self._peer_seq, self._peer_seq + 1
+        dev.plugin.check(self._peer_sum_unsplit(dev.index, x_local.buffer.ptr, x_local.numel(), first_index, n_total, 1 if mean else 0, seq,
+                                                out.buffer.ptr), "sharded sum in unsplit order")
+        note = getattr(dev.plugin, "peer_reduce", None)  # a recorder writes the call down (replay.Recorder)
+        if note is not None:
+            note(dev.index, 5 if mean else 4, x_local.buffer.ptr, x_local.numel(), first_index, n_total, out.buffer.ptr, out.dtype)
+        return out
+
+    def sum(self, x_local: Tensor, first_index: Optional[int] = None, n_total: Optional[int] = None) -> Tensor:
+        """Full-tensor sum. Given where this rank's shard starts in the flattened tensor and the
+        tensor's size, and shards of whole 65536-element blocks (``unsplit_order``), every rank chains
+        ALL block sums in block order: the bits of the sum over the unsplit tensor, whatever the number
+        of ranks. Otherwise every rank's ``Tensor.sum`` partial, combined in rank order."""
+        if first_index is not None and n_total is not None and self.unsplit_order(n_total):
+            return self._peer_unsplit(x_local, first_index, n_total, False)
         if self._peer_reduce:
             return self._peer(0, x_local)
         return self._defer(lambda: [x_local.raw_reshape([x_local.numel()]).raw_sum_axis(0)], [], DTYPE_F32, self._combine(op.SUM_AXIS))
 
-    def mean(self, x_local: Tensor, n_global: int) -> Tensor:
-        """``Tensor.mean`` of the reference: the sum, then a DIV by the element count as a scalar tensor."""
+    def mean(self, x_local: Tensor, n_global: int, first_index: Optional[int] = None) -> Tensor:
+        """``Tensor.mean`` of the reference: the sum, then a DIV by the element count as a scalar tensor.
+        With ``first_index`` and block-aligned shards the sum is taken in unsplit order (see ``sum``)."""
+        if first_index is not None and self.unsplit_order(n_global):
+            return self._peer_unsplit(x_local, first_index, n_global, True)
         if self._peer_reduce:  # the DIV by the f32 count runs in the combining kernel: the same bits, one launch instead of three
             return self._peer(3, x_local, 0, n_global)
 

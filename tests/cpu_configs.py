@@ -4,7 +4,7 @@ The oracle is a C++ restatement of the reference's CPU plugin; this script runs 
 ``python -m pytorches_b200.configs`` issues to the B200 plugin against it, on this host's cores, so
 that a CPU figure can stand beside each GPU figure. It is a reported baseline, not a target.
 
-Usage:  python oracle/time_configs.py [--config 1,3,4,4t] [--iters 3]
+Usage:  python tests/cpu_configs.py [--config 1,3,4,4t] [--iters 3]
 """
 
 from __future__ import annotations

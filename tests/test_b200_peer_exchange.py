@@ -80,6 +80,36 @@ def test_pointers_inside_a_buffer_take_the_narrow_load_kernels(b200, n):
     b200.synchronize(0)
 
 
+@pytest.mark.parametrize("n", [65536, 65536 * 3 + 5, 65536 * 200, (1 << 24) + 65536 * 3 + 1])
+def test_single_rank_group_sums_in_unsplit_order(b200, n):
+    """The sharded sum 'in unsplit order' with one rank: every block sum goes through the window's block
+    area and the chain over them must give SUM_AXIS's bits, call after call (more calls than generations)."""
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange(), b200.last_error()
+    assert g.unsplit_order(n)
+    t = Tensor.from_numpy(lcg_data(n, 13), dev)
+    for _ in range(6):
+        assert g.sum(t, 0, n).numpy().tobytes() == t.sum().numpy().tobytes()
+        assert g.mean(t, n, 0).numpy().tobytes() == t.mean().numpy().tobytes()
+
+
+def test_unsplit_order_needs_whole_blocks(b200):
+    import ctypes as C
+
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 2)  # two ranks on paper: only the rule is asked here
+    g._peer_reduce = object()
+    assert g.unsplit_order(65536 * 8) and g.unsplit_order(65536 * 8 + 2 * 17) is False  # 2 x (4 blocks + 17): rank 1 would start inside a block
+    assert not g.unsplit_order(65536)  # rank 1 would hold nothing
+    fn = b200.lib.pytorches_b200_peer_sum_unsplit
+    fn.restype = C.c_int32
+    fn.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_void_p]
+    t = Tensor.from_numpy(lcg_data(70000, 1), dev)
+    out = Tensor.zeros_on([1], dev)
+    assert fn(0, t.buffer.ptr, 70000, 100, 1 << 20, 0, 0, out.buffer.ptr) == abi.STATUS_INVALID_ARGUMENT and "65536" in b200.last_error()
+
+
 def test_column_sums_wider_than_the_window_are_refused(b200):
     import ctypes as C
 

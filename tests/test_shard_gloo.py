@@ -93,6 +93,25 @@ def _worker(rank: int, world: int, port: int, n: int, backend: str = "gloo"):
                 assert bits(g.mean(local, n).numpy()) == bits(np.float32(want_sum) / np.float32(n))
                 assert bits(g.max(local).numpy()) == bits(full.max().numpy())
                 assert g.argmax(local, start).numpy() == n // 2
+            # Shards of whole 65536-element blocks: the sum is taken in UNSPLIT order and has the bits of the
+            # oracle's sum over the whole tensor (and the mean those of its mean), several in a row.
+            nb = 65536 * 2 * world * 3 + 777 if n > 1 << 20 else 0
+            if nb:
+                xb = lcg_data(nb, 19)
+                per = 65536 * 2 * 3
+                lo, cnt = (rank * per, per) if rank < world - 1 else (rank * per, nb - rank * per)
+                class _Even(ShardGroup):  # the benchmark's even split: the last rank takes the ragged tail
+                    def unsplit_order(self, n_total):
+                        return self.peer_exchange
+                ge = _Even.__new__(_Even)
+                ge.__dict__.update(g.__dict__)
+                shard = Tensor.from_numpy(xb[lo:lo + cnt], gdev)
+                whole = Tensor.from_numpy(xb, dev)
+                for _ in range(5):
+                    assert bits(ge.sum(shard, lo, nb).numpy()) == bits(whole.sum().numpy())
+                    assert bits(ge.mean(shard, nb, lo).numpy()) == bits(whole.mean().numpy())
+                    assert ge.argmax(shard, lo).numpy() == whole.argmax().numpy()
+                g._peer_seq = ge._peer_seq  # one sequence for the group: the next reduction continues it
             small = Tensor.from_numpy(x[start:start + 5], gdev)  # a shard too short for a combiner CTA: separate exchange launch
             want_small = sum((x[split_rows(n, r, world)[0]:][:5].astype(np.float64).sum() for r in range(world)))
             assert abs(float(g.sum(small).numpy()) - want_small) < 1e-4
