@@ -115,14 +115,19 @@ size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint6
 // GPUs); its worker CTAs are long done by then. Such a kernel signals early that dependents may
 // launch, and if the NEXT thing enqueued is again such a reduction with buffers disjoint from this
 // one's, it is launched with programmatic stream serialization: its workers stream while this one's
-// combiner finishes. Ordering is kept where it matters: a combiner first waits for the previous
-// kernel to complete, and only then lets the kernel after its own start, so at most two such kernels
-// are ever in flight and they complete in order; any other kind of work is launched normally and
-// starts after everything before it has completed. `tail_open` is false after anything else.
+// combiner finishes. Ordering is kept where it matters: a combiner lets the kernel after its own
+// start only when the combiner two launches back has finished, and finishes only after the kernel
+// before its own has completed. So at most three such kernels are at work (one chaining, one
+// streaming, one starting), they complete in launch order, and a launch must be disjoint from the
+// two before it. Any other kind of work is launched normally and starts after everything before it
+// has completed; `tail_open` is false after anything else.
 struct LaunchChain {
-    bool tail_open = false;
-    const char *in_lo = nullptr, *in_hi = nullptr;  // the open reduction's input range
-    const void *out[2] = {nullptr, nullptr};        // and its outputs
+    struct Open {
+        const char *in_lo = nullptr, *in_hi = nullptr;  // an unfinished reduction's input range
+        const void *out[2] = {nullptr, nullptr};        // and its outputs
+    };
+    bool tail_open = false;  // the newest launch on the stream is such a reduction
+    Open last, before_last;  // it, and the one launched before it if that one may be unfinished too (else all null)
 };
 
 // With `px` (only for outer == inner == 1): the result written is the combination over all ranks, in

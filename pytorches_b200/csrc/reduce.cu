@@ -136,6 +136,44 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
 __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void wait_for_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+constexpr uint32_t POLL_LIMIT = 1u << 21;  // polls of a mailbox word (or of `done`) before giving up
+
+// How the combiner CTAs of back-to-back reductions keep order while up to THREE of these kernels are
+// in flight. `done` is a per-device word holding the launch number (`epoch`, consecutive per device)
+// of the newest such kernel that has finished. A combiner
+//   * begins by waiting (bounded) until the kernel two before its own has finished, and only then
+//     lets the kernel after its own start: kernels e-1, e and e+1 may overlap, e+2 may not start
+//     before e-1 is done, so four mailbox regions and eight window generations used in turn never
+//     collide (a rank cannot finish a reduction without every peer's part, which bounds the skew);
+//   * works (polls, chains, exchanges) at once, whatever the kernels before it are doing: the chain of
+//     a sum in unsplit order, 4096 dependent adds, thus has two kernels' streaming to hide behind;
+//   * ends by waiting for the kernel before its own to complete (griddepcontrol.wait) and then
+//     publishing its number: completion is in launch order, so whatever is launched the ordinary way
+//     after these kernels, waiting for the last, waits for all of them.
+// A wait that runs out is reported through *status like every other bounded wait; the combiner still
+// lets its dependents start and still publishes its number, so one failure does not stall the stream.
+__device__ __forceinline__ void combiner_begin(unsigned long long *done, uint32_t epoch, int *status) {
+    bool ok = false;
+    for (uint32_t tries = 0; tries < POLL_LIMIT; ++tries) {
+        unsigned long long d;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(d) : "l"(done) : "memory");
+        if ((long long)(d + 2 - (unsigned long long)epoch) >= 0) {
+            ok = true;
+            break;
+        }
+    }
+    if (!ok && (threadIdx.x & 31) == 0) {
+        *(volatile int *)status = STATUS_WAIT_EXPIRED;
+        __threadfence_system();
+    }
+    launch_dependents();
+}
+// One thread of the combiner CTA calls this after everything else the CTA does.
+__device__ __forceinline__ void combiner_end(unsigned long long *done, uint32_t epoch) {
+    wait_for_prior_grid();
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(done), "l"((unsigned long long)epoch) : "memory");
+}
+
 // FUSED (one row only): the ordered chain over the block sums runs INSIDE this launch. CTA 0 is the
 // combiner; CTAs 1..blocks are the workers. A worker publishes its block sum as ONE 64-bit word,
 // (epoch << 32) | float bits, into a per-device mailbox; the combiner polls the words in block order
@@ -145,7 +183,6 @@ __device__ __forceinline__ void wait_for_prior_grid() { asm volatile("griddepcon
 // in waves and the chain hides behind the streaming; only the last wave's sums are added after it.
 // A 64-bit aligned store is indivisible, so no fence and no atomic is needed, and the order of the
 // adds (hence the bits) is the reference's. The combiner's polls are bounded like every other wait.
-constexpr uint32_t POLL_LIMIT = 1u << 21;
 
 __device__ __forceinline__ unsigned long long ld_mailbox(const unsigned long long *p) {
     unsigned long long v;
@@ -166,12 +203,13 @@ __device__ __forceinline__ bool vi_better(float v, uint64_t i, float bv, uint64_
 // stores it into slot `rank` of rank r's window (its own window included) and then waits for slot r
 // of its OWN window to be filled by rank r. A slot is two 64-bit words: the position, written first,
 // then (epoch << 32) | float bits, written with release semantics at system scope; the reader polls
-// that word with acquire loads until it carries this reduction's epoch. Four generations of slots are
-// used in turn, so a fast rank's next reduction never lands on a slot a slow rank has yet to read (to
-// run two reductions ahead a rank would need the slow rank's result of the one in between).
+// that word with acquire loads until it carries this reduction's epoch. Eight generations of slots are
+// used in turn, so a fast rank's later reduction never lands on a slot a slow rank has yet to read: a
+// rank starts reduction s only after its own combiner of s-3 has finished (see combiner_begin), which
+// needed every peer's part of s-3, and a peer working on s-3 has finished reading everything up to s-6.
 // The wait is bounded in time; if a peer never shows up the warp records it in *status and returns
 // false without a result, and the host reports the failure at its next blocking call.
-constexpr int PEER_GENERATIONS = 4;
+constexpr int PEER_GENERATIONS = 8;
 constexpr int PEER_SLOT_WORDS = 2;
 constexpr size_t PEER_WINDOW_WORDS = (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_SLOT_WORDS;
 constexpr int STATUS_PEER_WAIT_EXPIRED = 2;
@@ -358,14 +396,9 @@ __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_const
 // once the words are there), and re-polls only the words not yet published.
 constexpr int COMBINER_WORDS = 16;
 
-__device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
-                                 const PeerXchg &px, float *stage) {
+__device__ void ordered_combiner_body(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
+                                      const PeerXchg &px, float *stage) {
     const int lane = threadIdx.x;
-    // The kernel before this one (if this one was allowed to start early) completes first; only then
-    // may the kernel after this one start. So at most two of these kernels are in flight, they finish
-    // in stream order, and mailbox regions and peer-window generations, used in turn, never collide.
-    wait_for_prior_grid();
-    launch_dependents();
     float s = 0.0f;
     // In unsplit order the words are this rank's window, written by every rank's workers: loads at
     // system scope, and the patience of a wait for peers (time, not tries).
@@ -459,6 +492,15 @@ __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epo
     if (lane == 0) out[0] = s;
 }
 
+// `launch_no`: this kernel's number among the device's chained reductions (see combiner_begin).
+__device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
+                                 const PeerXchg &px, float *stage, unsigned long long *done, uint32_t launch_no) {
+    combiner_begin(done, launch_no, status);
+    ordered_combiner_body(mailbox, epoch, blocks, out, status, px, stage);
+    __syncwarp();
+    if (threadIdx.x == 0) combiner_end(done, launch_no);
+}
+
 // Unsplit order, second special CTA: hands this GPU's block sums to every rank. The workers publish
 // into the local mailbox exactly as they do on one GPU (a store across NVLink at the end of a worker
 // would keep its SM slot busy for the round trip, 1024 times per reduction); this warp polls the local
@@ -501,7 +543,7 @@ __device__ void block_forwarder(const unsigned long long *mailbox, uint32_t epoc
 template <bool FUSED, int STAGES, uint32_t CHUNK>
 __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restrict__ x, uint64_t tasks, uint64_t len, uint64_t blocks,
                                                           float *__restrict__ dst, int *status, unsigned long long *mailbox, uint32_t epoch,
-                                                          const __grid_constant__ PeerXchg px, uint32_t ordered) {
+                                                          const __grid_constant__ PeerXchg px, uint32_t ordered, unsigned long long *done) {
     constexpr uint32_t CHUNK_BYTES = CHUNK * 4;
     extern __shared__ __align__(128) unsigned char tma_smem[];
     __shared__ uint64_t bars[STAGES];
@@ -510,9 +552,9 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
         if (px.blocks_total != 0) {  // unsplit order: chain the whole tensor's block sums out of this rank's own window
             const unsigned long long *mine = own_window(px);
             return ordered_combiner(mine + PEER_BLOCK_AREA_WORD + (size_t)(px.epoch % PEER_GENERATIONS) * PEER_BLOCKS_MAX, px.epoch, px.blocks_total, dst,
-                                    status, px, ring);
+                                    status, px, ring, done, epoch);
         }
-        return ordered_combiner(mailbox, epoch, blocks, dst, status, px, ring);
+        return ordered_combiner(mailbox, epoch, blocks, dst, status, px, ring, done, epoch);
     }
     // `ordered`: what came before in the stream may have written this kernel's input, so it waits for
     // that to complete like every other kernel. Otherwise (the kernel before is a reduction of other
@@ -917,16 +959,14 @@ constexpr int MAX_UNROLL = 4;
 // AFTER the segment's position has been written to `seg_pos`), keeps the best (value, segment) pair -
 // NaN wins, then the larger value, then the lower segment - and writes the row's result. Max is
 // order-free, so all 256 threads poll and scan in parallel; polls are bounded.
-__device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v,
-                             int64_t *out_i, int64_t idx_offset, int *status, const PeerXchg &px) {
+__device__ void max_combiner_body(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v,
+                                  int64_t *out_i, int64_t idx_offset, int *status, const PeerXchg &px) {
     __shared__ float sv[8];
     __shared__ uint64_t ss[8];
     constexpr int WORDS = 8;
     float bv = __int_as_float(0xff800000);
     uint64_t bs = ~0ull;
     bool failed = false;
-    wait_for_prior_grid();  // same ordering rule as the sum's combiner
-    launch_dependents();
     for (uint64_t base = 0; base < segs; base += (uint64_t)MAX_CTA * WORDS) {
         float v[WORDS];
         uint32_t missing = 0;
@@ -994,6 +1034,14 @@ __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, 
     }
 }
 
+__device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v, int64_t *out_i,
+                             int64_t idx_offset, int *status, const PeerXchg &px, unsigned long long *done) {
+    combiner_begin(done, epoch, status);  // same ordering rules as the sum's combiner
+    max_combiner_body(mailbox, epoch, segs, seg_pos, out_v, out_i, idx_offset, status, px);
+    __syncthreads();
+    if (threadIdx.x == 0) combiner_end(done, epoch);
+}
+
 // What a fused launch adds to max_rows_kernel's arguments (mailbox == nullptr: the plain two-pass form).
 struct MaxFused {
     unsigned long long *mailbox;
@@ -1004,6 +1052,7 @@ struct MaxFused {
     int *status;
     PeerXchg px;
     int ordered;  // workers wait for the kernel before this one to complete before they read (see sum_rows_tma_kernel)
+    unsigned long long *done;  // the device's word of finished launch numbers (see combiner_begin)
 };
 
 // inner == 1. Task t = (row, seg): elements [seg*seg_len, min(len, (seg+1)*seg_len)) of row. TPT
@@ -1016,7 +1065,7 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
                                                            int64_t *__restrict__ out_i, int64_t idx_offset, const __grid_constant__ MaxFused fused) {
     constexpr int PER_CTA = MAX_CTA / TPT;
     if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
-        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px);
+        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px, fused.done);
     if (TPT == MAX_CTA && fused.mailbox != nullptr && !fused.ordered) launch_dependents();
     else ordered_start();
     const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
@@ -1233,16 +1282,17 @@ namespace {
 // The in-launch combiners' mailbox: MAILBOX_REGIONS regions per device, each MAILBOX_SLOTS 64-bit
 // value words followed by as many 64-bit position words (the max/argmax combiner reads a segment's
 // position there), allocated and zeroed on first use and kept for the life of the process. Each
-// launch gets the next epoch (never 0) and the region epoch mod MAILBOX_REGIONS: two launches may be
-// in flight at once (see LaunchChain), never more, so a region is not written again before its last
-// reader is done. When the 32-bit epoch wraps the words are zeroed again, on the stream, so no stale
+// launch gets the next epoch (never 0) and the region epoch mod MAILBOX_REGIONS: launch e+4 starts
+// only after the combiner of e+1 has finished, which is after launch e has completed (see
+// combiner_begin), so a region is not written again before its last reader is done. The word after
+// the regions is `done`, the number of the newest launch whose combiner has finished. When the 32-bit epoch wraps the words are zeroed again, on the stream, so no stale
 // word can match.
 constexpr uint64_t MAILBOX_SLOTS = 1ull << 18;  // a sum's row of up to 2^34 elements, a max's of up to 2^32
 constexpr int MAILBOX_REGIONS = 4;
-constexpr size_t MAILBOX_BYTES = (size_t)MAILBOX_REGIONS * MAILBOX_SLOTS * 2 * 8;
+constexpr size_t MAILBOX_BYTES = (size_t)MAILBOX_REGIONS * MAILBOX_SLOTS * 2 * 8 + 256;  // + the word of finished launch numbers
 // PYTORCHES_B200_FUSED_COMBINE=0 in the environment turns the in-launch combines off (two launches
 // per reduction instead of one); a diagnostic switch, read once.
-unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
+unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch, unsigned long long **done) {
     static const bool enabled = [] {
         const char *e = getenv("PYTORCHES_B200_FUSED_COMBINE");
         return !(e && e[0] == '0');
@@ -1270,6 +1320,7 @@ unsigned long long *mailbox_for(int device, cudaStream_t s, uint32_t *epoch) {
         next[device] = 1;
     }
     *epoch = next[device];
+    *done = box[device] + (size_t)MAILBOX_REGIONS * MAILBOX_SLOTS * 2;
     return box[device] + (size_t)(next[device] % MAILBOX_REGIONS) * MAILBOX_SLOTS * 2;
 }
 
@@ -1361,7 +1412,7 @@ bool make_cols_tensor_map(CUtensorMap *map, const float *x, uint64_t rows, uint6
 // again, so that epochs may restart with a new group of ranks. Peers' windows are opened once per
 // handle and never closed.
 namespace {
-constexpr size_t PEER_WINDOW_BYTES = size_t(2) << 20;
+constexpr size_t PEER_WINDOW_BYTES = size_t(4) << 20;
 static_assert(PEER_WINDOW_WORDS <= PEER_VECTOR_AREA_WORD, "the scalar slots end before the vector area");
 static_assert((PEER_BLOCK_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_BLOCKS_MAX) * 8 <= PEER_WINDOW_BYTES, "the vector and block areas fit the window");
 struct PeerWindows {
@@ -1482,28 +1533,32 @@ size_t reduce_scratch_bytes(ReduceKind kind, uint64_t outer, uint64_t len, uint6
 namespace {
 bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
-// May a reduction of [x, x + n) into out_v / out_i start while the reduction `c` describes is still
-// finishing? Only if neither touches what the other writes.
+// May a reduction of [x, x + n) into out_v / out_i start while the reductions `c` describes are still
+// finishing? Only if it touches nothing that they write and writes nothing that they touch.
 bool may_overlap(const LaunchChain *c, const float *x, uint64_t n, const void *out_v, const void *out_i) {
     if (!c || !c->tail_open || !overlap_enabled()) return false;
     const char *lo = (const char *)x, *hi = lo + n * sizeof(float);
-    for (const void *o : c->out) {
-        if (!o) continue;
-        if ((const char *)o >= lo && (const char *)o < hi) return false;  // it writes into our input
-        if (o == out_v || o == out_i) return false;                       // both write the same word: order would matter
+    for (const LaunchChain::Open *open : {&c->last, &c->before_last}) {
+        for (const void *o : open->out) {
+            if (!o) continue;
+            if ((const char *)o >= lo && (const char *)o < hi) return false;  // it writes into our input
+            if (o == out_v || o == out_i) return false;                       // both write the same word: order would matter
+        }
+        for (const void *o : {out_v, out_i})
+            if (o && (const char *)o >= open->in_lo && (const char *)o < open->in_hi) return false;  // we write into its input
     }
-    for (const void *o : {out_v, out_i})
-        if (o && (const char *)o >= c->in_lo && (const char *)o < c->in_hi) return false;  // we write into its input
     return true;
 }
 
-void chain_opened(LaunchChain *c, const float *x, uint64_t n, const void *out_v, const void *out_i) {
+// `early`: this launch was allowed to start before `prev`'s newest one completed, so that one stays on the list.
+void chain_opened(const LaunchChain *prev, LaunchChain *c, bool early, const float *x, uint64_t n, const void *out_v, const void *out_i) {
     if (!c) return;
     c->tail_open = true;
-    c->in_lo = (const char *)x;
-    c->in_hi = c->in_lo + n * sizeof(float);
-    c->out[0] = out_v;
-    c->out[1] = out_i;
+    c->before_last = early && prev ? prev->last : LaunchChain::Open{};
+    c->last.in_lo = (const char *)x;
+    c->last.in_hi = c->last.in_lo + n * sizeof(float);
+    c->last.out[0] = out_v;
+    c->last.out[1] = out_i;
 }
 
 // The local reduction. With `px`, a launch that ends in a combiner CTA also does the cross-GPU step
@@ -1536,7 +1591,8 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
             if (status && staged_kernels_ready(device)) {
                 // A single long row: chain the block sums inside the same launch (see ordered_combiner).
                 uint32_t epoch = 0;
-                unsigned long long *mailbox = (outer == 1 && (blocks >= 64 || unsplit) && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch) : nullptr;
+                unsigned long long *done = nullptr;
+                unsigned long long *mailbox = (outer == 1 && (blocks >= 64 || unsplit) && blocks <= MAILBOX_SLOTS) ? mailbox_for(device, s, &epoch, &done) : nullptr;
                 if (unsplit && !mailbox) return cudaErrorInvalidValue;
                 const int ring = pick_ring(tasks, sm_count(device));
                 const bool early = mailbox && may_overlap(prev, x, len, o, nullptr);
@@ -1545,17 +1601,17 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         if (mailbox)                                                                                                                        \
             B200_LAUNCH_ORDERED((sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + (unsplit ? 2 : 1), 32,       \
                                 ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, o, status, mailbox, epoch,           \
-                                px ? *px : no_peers, early ? 0u : 1u);                                                                      \
+                                px ? *px : no_peers, early ? 0u : 1u, done);                                                                \
         else                                                                                                                                \
             B200_LAUNCH_ORDERED((sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks, 32,                         \
                                 ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, dst, status,                         \
-                                (unsigned long long *)nullptr, 0u, no_peers, 1u);                                                           \
+                                (unsigned long long *)nullptr, 0u, no_peers, 1u, (unsigned long long *)nullptr);                            \
     }
                 B200_RING_CASE(0) B200_RING_CASE(1) B200_RING_CASE(2) B200_RING_CASE(3) B200_RING_CASE(4)
 #undef B200_RING_CASE
                 if (mailbox) {
                     *peer_done = px != nullptr;
-                    chain_opened(next, x, len, o, nullptr);
+                    chain_opened(prev, next, early, x, len, o, nullptr);
                     return cudaGetLastError();
                 }
             } else {
@@ -1618,10 +1674,11 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     if (outer == 1 && m.tpt == MAX_CTA && m.segs >= 64 && m.segs <= MAILBOX_SLOTS) {
         int *status = reduce_status_word(device);
         uint32_t epoch = 0;
-        unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch) : nullptr;
+        unsigned long long *done = nullptr;
+        unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch, &done) : nullptr;
         if (mailbox) {
             early = may_overlap(prev, x, len, ov, oi);
-            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers, early ? 0 : 1};
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers, early ? 0 : 1, done};
             grid += 1;
             *peer_done = px != nullptr;
         }
@@ -1646,7 +1703,7 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     B200_MAX_CASE(256, 1)
     B200_MAX_CASE(256, 4)
 #undef B200_MAX_CASE
-    if (fused.mailbox) chain_opened(next, x, len, ov, oi);
+    if (fused.mailbox) chain_opened(prev, next, early, x, len, ov, oi);
     if (m.segs > 1 && !fused.mailbox) B200_LAUNCH_ORDERED(max_combine_kernel, (unsigned)outer, 256, 0, s, pv, pi, outer, m.segs, ov, oi, idx_offset);
     return cudaGetLastError();
 }
