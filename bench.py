@@ -444,12 +444,16 @@ def run(args, plugin, rank, world, local, torch, dist, Device, Tensor, Recorder,
             if world > 1 and group.peer_exchange and os.environ.get("PYTORCHES_B200_PEER_TRACE") == "1":  # where the sharded reductions' time went, by the device's clock
                 rec_t, last = group.peer_trace().astype(np.int64), group.peer_seq
                 trace = {}
+                rec_of = lambda q: rec_t[(q % 0xfffffffe + 1) % 64]
                 for j, name in enumerate(OPS):  # reduction number q is op q % 4 of a step; its record is (q % 0xfffffffe + 1) % 64
-                    rows = [rec_t[(q % 0xfffffffe + 1) % 64] for q in range(max(last - 64, 0), last) if q % len(OPS) == j]
-                    rows = [r for r in rows if r[1:].min() > 0 and r[3] >= r[2] >= r[1]]
-                    if rows:
-                        trace[name] = {"wait_for_slowest_peer_us": round(statistics.median((r[2] - r[1]) / 1e3 for r in rows), 2),
-                                       "after_last_arrival_us": round(statistics.median((r[3] - r[2]) / 1e3 for r in rows), 2)}
+                    qs = [q for q in range(max(last - 60, 1), last) if q % len(OPS) == j and rec_of(q)[1:4].min() > 0 and rec_of(q - 1)[3] > 0]
+                    if not qs:
+                        continue
+                    med = lambda f: round(statistics.median(f(rec_of(q)) / 1e3 for q in qs), 2)
+                    trace[name] = {"wait_for_slowest_peer_us": med(lambda r: r[2] - r[1]), "after_last_arrival_us": med(lambda r: r[3] - r[2]),
+                                   "result_after_previous_result_us": round(statistics.median((rec_of(q)[3] - rec_of(q - 1)[3]) / 1e3 for q in qs), 2)}
+                    if all(rec_of(q)[13] > 0 for q in qs):  # a sum in unsplit order: bulk copies of the block sums its combiner needed
+                        trace[name]["combiner_copies"] = int(statistics.median(int(rec_of(q)[13]) for q in qs))
             # after the timed region: one more step, read back, must still be the gate's values
             same = all(a.numpy().tobytes() == b.tobytes() for a, b in zip(step(rotating), res))
             if not same:

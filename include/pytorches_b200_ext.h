@@ -137,13 +137,14 @@ int32_t pytorches_b200_peer_sum_unsplit(uint32_t device, const float *x, uint64_
 /*
  * Where the time of the sharded reductions goes (a diagnostic: set PYTORCHES_B200_PEER_TRACE=1 in the
  * environment before the windows are attached; off by default because the extra stores were measured
- * to disturb multi-GPU runs). Every reduction with an in-kernel exchange then leaves four device-clock
+ * to disturb multi-GPU runs). Every reduction with an in-kernel exchange then leaves device-clock
  * readings (nanoseconds, %globaltimer) in a per-device buffer, in record
- * (seq % 0xfffffffe + 1) % 64: [1] this GPU's own part is complete, [2] every rank's part has
- * arrived, [3] the result is written ([0] is unused).
+ * (seq % 0xfffffffe + 1) % 64 of sixteen words: [1] this GPU's own part is complete, [2] every rank's
+ * part has arrived, [3] the result is written; a sum in unsplit order also leaves [13], how many bulk
+ * copies of the block sums its combiner needed (a count, not a time). The other words are unused.
  * [2] - [1] is the wait for the slowest peer (skew between the GPUs plus NVLink latency), [3] - [2]
  * the work left after the last arrival. This call synchronizes the device's stream and copies the 64
- * records (64 x 4 uint64) to `records_out`. Replaces nothing in the reference.
+ * records (64 x 16 uint64) to `records_out`. Replaces nothing in the reference.
  */
 int32_t pytorches_b200_peer_trace(uint32_t device, uint64_t *records_out);
 

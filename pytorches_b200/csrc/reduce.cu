@@ -122,10 +122,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-// Bulk copy from global memory into this CTA's own shared memory.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+// Bulk copy from global memory into this CTA's own shared memory. `policy` (read_once_policy): the
+// data is read once, so L2 may drop it first. A reduction streams its whole input through L2; left at
+// normal priority that pushes out the few lines everything else waits on (the combiners' mailbox and
+// window words), and a combiner that has to fetch them from DRAM again queues behind megabytes of
+// bulk copies in flight: several microseconds per look.
+__device__ __forceinline__ uint64_t read_once_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
                  : "memory");
 }
 
@@ -152,12 +161,12 @@ constexpr uint32_t POLL_LIMIT = 1u << 21;  // polls of a mailbox word (or of `do
 //     after these kernels, waiting for the last, waits for all of them.
 // A wait that runs out is reported through *status like every other bounded wait; the combiner still
 // lets its dependents start and still publishes its number, so one failure does not stall the stream.
-__device__ __forceinline__ void combiner_begin(unsigned long long *done, uint32_t epoch, int *status) {
+__device__ __forceinline__ void combiner_begin(unsigned long long *done, uint32_t epoch, int *status, uint32_t lag) {
     bool ok = false;
     for (uint32_t tries = 0; tries < POLL_LIMIT; ++tries) {
         unsigned long long d;
         asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(d) : "l"(done) : "memory");
-        if ((long long)(d + 2 - (unsigned long long)epoch) >= 0) {
+        if ((long long)(d + lag - (unsigned long long)epoch) >= 0) {
             ok = true;
             break;
         }
@@ -331,15 +340,17 @@ constexpr size_t PEER_VECTOR_AREA_WORD = 512;        // first word of the vector
 constexpr uint32_t PEER_BLOCKS_MAX = 16384;
 constexpr size_t PEER_BLOCK_AREA_WORD = PEER_VECTOR_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_MAX_RANKS * PEER_VECTOR_MAX;
 // Beside the window, in ordinary memory of the device: a trace of its last PEER_TRACE_RECORDS reductions,
-// four words each (record = epoch mod PEER_TRACE_RECORDS), %globaltimer readings: [1] this GPU's own
-// part is complete (its result ready to send, or its last block sum forwarded), [2] every rank's part
-// has arrived here, [3] the result is written; [0] is unused. [2] - [1] is the wait for the slowest
+// PEER_TRACE_WORDS words each (record = epoch mod PEER_TRACE_RECORDS), %globaltimer readings: [1] this
+// GPU's own part is complete (its result ready to send, or its last block sum forwarded), [2] every
+// rank's part has arrived here, [3] the result is written; a sum in unsplit order adds [13], the
+// number of bulk copies its combiner needed (a count); the rest is unused. [2] - [1] is the wait for the slowest
 // peer (skew plus NVLink latency; in unsplit order it also holds this combiner's wait for the kernel
 // before it), [3] - [2] what is left to do after the last arrival. Read back with
 // pytorches_b200_peer_trace. (A reading at the combiner's start was dropped: a store placed right
 // behind griddepcontrol.launch_dependents, even one that never executes, cost 12% of the step at 2
 // GPUs and 40% at 4 with sums in unsplit order.)
 constexpr uint32_t PEER_TRACE_RECORDS = 64;
+constexpr uint32_t PEER_TRACE_WORDS = 16;
 
 __device__ __forceinline__ unsigned long long *own_window(const PeerXchg &px) {
     unsigned long long *mine = px.window[0];
@@ -349,7 +360,7 @@ __device__ __forceinline__ unsigned long long *own_window(const PeerXchg &px) {
     return mine;
 }
 __device__ __forceinline__ void peer_trace(const PeerXchg &px, int what) {
-    if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * 4 + what] = global_ns();
+    if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * PEER_TRACE_WORDS + what] = global_ns();
 }
 
 __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_constant__ PeerXchg px, const float *__restrict__ partial, uint32_t m,
@@ -396,20 +407,48 @@ __global__ void __launch_bounds__(256) peer_vector_sum_kernel(const __grid_const
 // once the words are there), and re-polls only the words not yet published.
 constexpr int COMBINER_WORDS = 16;
 
+// s + f[0] + f[1] + ... + f[n-1], in that order, out of shared memory: every lane runs the same chain
+// with 16-byte broadcast loads, four sums per load, the next loads in flight while the current four
+// adds run, so the chain advances at the add latency. `f` is 16-byte aligned; up to 16 floats past
+// f[n-1] are read and dropped, so they must lie inside the CTA's shared memory.
+__device__ __forceinline__ float chain_staged(const float *f, uint32_t n, float s) {
+    const float4 *quad = reinterpret_cast<const float4 *>(f);
+    float4 cur[4], nxt[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) cur[u] = quad[u];
+    uint32_t i = 0;
+    for (; i + 32 <= n; i += 32) {  // 32 sums per trip: two batches of four float4
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            nxt[u] = quad[i / 4 + 4 + u];
+            s = __fadd_rn(s, cur[u].x);
+            s = __fadd_rn(s, cur[u].y);
+            s = __fadd_rn(s, cur[u].z);
+            s = __fadd_rn(s, cur[u].w);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            cur[u] = quad[i / 4 + 8 + u];
+            s = __fadd_rn(s, nxt[u].x);
+            s = __fadd_rn(s, nxt[u].y);
+            s = __fadd_rn(s, nxt[u].z);
+            s = __fadd_rn(s, nxt[u].w);
+        }
+    }
+    for (; i < n; ++i) s = __fadd_rn(s, f[i]);
+    return s;
+}
+
 __device__ void ordered_combiner_body(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
                                       const PeerXchg &px, float *stage) {
     const int lane = threadIdx.x;
     float s = 0.0f;
-    // In unsplit order the words are this rank's window, written by every rank's workers: loads at
-    // system scope, and the patience of a wait for peers (time, not tries).
-    const bool unsplit = px.blocks_total != 0;
-    const unsigned long long t0 = unsplit ? global_ns() : 0, limit = (unsigned long long)px.wait_ms * 1000000ull;
     constexpr uint64_t ROUND = 32 * COMBINER_WORDS;
     unsigned long long w[COMBINER_WORDS];  // the round whose loads are in flight
     auto issue = [&](uint64_t base) {
 #pragma unroll
         for (int k = 0; k < COMBINER_WORDS; ++k)
-            if (base + k * 32 + lane < blocks) w[k] = unsplit ? ld_mailbox_sys(mailbox + base + k * 32 + lane) : ld_mailbox(mailbox + base + k * 32 + lane);
+            if (base + k * 32 + lane < blocks) w[k] = ld_mailbox(mailbox + base + k * 32 + lane);
     };
     issue(0);
     for (uint64_t base = 0; base < blocks; base += ROUND) {
@@ -423,12 +462,11 @@ __device__ void ordered_combiner_body(const unsigned long long *mailbox, uint32_
                 else missing |= 1u << k;
             }
         }
-        for (uint32_t tries = 0; (unsplit || tries < POLL_LIMIT) && __any_sync(0xffffffffu, missing != 0); ++tries) {
-            if (unsplit && (tries & 63) == 63 && __any_sync(0xffffffffu, global_ns() - t0 > limit)) break;
+        for (uint32_t tries = 0; tries < POLL_LIMIT && __any_sync(0xffffffffu, missing != 0); ++tries) {
             unsigned long long again[COMBINER_WORDS];
 #pragma unroll
             for (int k = 0; k < COMBINER_WORDS; ++k)
-                if (missing & (1u << k)) again[k] = unsplit ? ld_mailbox_sys(mailbox + base + k * 32 + lane) : ld_mailbox(mailbox + base + k * 32 + lane);
+                if (missing & (1u << k)) again[k] = ld_mailbox(mailbox + base + k * 32 + lane);
 #pragma unroll
             for (int k = 0; k < COMBINER_WORDS; ++k)
                 if ((missing & (1u << k)) && (uint32_t)(again[k] >> 32) == epoch) {
@@ -438,65 +476,149 @@ __device__ void ordered_combiner_body(const unsigned long long *mailbox, uint32_
         }
         if (__any_sync(0xffffffffu, missing != 0)) {
             if (lane == 0) {
-                *(volatile int *)status = unsplit ? STATUS_PEER_WAIT_EXPIRED : STATUS_WAIT_EXPIRED;
+                *(volatile int *)status = STATUS_WAIT_EXPIRED;
                 __threadfence_system();
             }
             return;
         }
         if (base + ROUND < blocks) issue(base + ROUND);  // in flight while this round is chained
-        else if (unsplit && lane == 0) peer_trace(px, 2);  // the last round's words are here: every rank's part has arrived
         // The round's sums go through shared memory (this CTA's ring is otherwise unused) so that every
         // lane can run the same chain with 16-byte broadcast loads, four sums per load, the next loads
         // in flight while the current four adds run: the chain advances at the add latency. (Fetching
-        // each sum from its lane with a shuffle costs five times that, which shows as soon as all
-        // sums are there at once, as they are when a tensor's blocks arrive from several GPUs.)
+        // each sum from its lane with a shuffle costs five times that.)
         __syncwarp();
 #pragma unroll
         for (int k = 0; k < COMBINER_WORDS; ++k) stage[k * 32 + lane] = v[k];
         __syncwarp();
         const uint32_t count = (uint32_t)(blocks - base < ROUND ? blocks - base : ROUND);
-        const float4 *quad = reinterpret_cast<const float4 *>(stage);
-        float4 cur[4], nxt[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) cur[u] = quad[u];
-        uint32_t i = 0;
-        for (; i + 32 <= count; i += 32) {  // 32 sums per trip: two batches of four float4
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                nxt[u] = quad[i / 4 + 4 + u];
-                s = __fadd_rn(s, cur[u].x);
-                s = __fadd_rn(s, cur[u].y);
-                s = __fadd_rn(s, cur[u].z);
-                s = __fadd_rn(s, cur[u].w);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                cur[u] = quad[(i / 4 + 8 + u) % (ROUND / 4)];  // past the end of the round: wraps to a valid address, the value is dropped
-                s = __fadd_rn(s, nxt[u].x);
-                s = __fadd_rn(s, nxt[u].y);
-                s = __fadd_rn(s, nxt[u].z);
-                s = __fadd_rn(s, nxt[u].w);
-            }
-        }
-        for (; i < count; ++i) s = __fadd_rn(s, stage[i]);
-    }
-    if (unsplit) {  // every rank has chained every block: nothing left to exchange
-        if (px.divide_by != 0.0f) s = __fdiv_rn(s, px.divide_by);
-        if (lane == 0) {
-            out[0] = s;
-            peer_trace(px, 3);
-        }
-        return;
+        s = chain_staged(stage, count, s);
     }
     if (px.world > 0) return peer_finish(px, REDUCE_SUM, s, 0, out, nullptr, status);  // s is the same in every lane
     if (lane == 0) out[0] = s;
 }
 
+// The combiner of a sum in unsplit order. `words` = this reduction's generation of the block area of
+// this rank's own window, one (epoch << 32 | bits) word per block of the WHOLE tensor, written by
+// every rank's forwarder. The chain over them is serial and must follow block order, and on G GPUs
+// all but the first GPU's last blocks are there long before their turn: when the last block sums
+// arrive, about (G-1)/G of the chain is still to run. What must not be paid then is a memory round
+// trip per few hundred words: under the streaming of the kernels that follow, a load that misses L2
+// queues behind megabytes of bulk copies, microseconds each time. So the words are fetched the way
+// the workers fetch their input: ONE bulk copy brings every word from the chain's position on (up to
+// UNSPLIT_WINDOW of them, 32 KiB) into shared memory; the warp finds how far the words of this
+// reduction reach without a gap, asks for the next copy into the other buffer, and chains what it
+// has out of shared memory meanwhile. After the last arrival that is at most two copies and one pass
+// of the chain. Waits are bounded: each copy by the barrier's try limit, the whole by px.wait_ms.
+constexpr uint32_t UNSPLIT_WINDOW = 4096;                                  // words per copy
+constexpr size_t UNSPLIT_SMEM = (size_t)2 * UNSPLIT_WINDOW * 8;            // two buffers
+// Dynamic shared memory of a fused launch: the workers' ring, and room for the unsplit combiner's buffers
+// (every CTA of a launch gets the same; 64 KiB still lets three CTAs share an SM).
+constexpr size_t fused_smem(int stages, uint32_t chunk, bool unsplit) {
+    return unsplit && ring_bytes(stages, chunk) < UNSPLIT_SMEM ? UNSPLIT_SMEM : ring_bytes(stages, chunk);
+}
+__device__ void unsplit_combiner(const unsigned long long *words, uint32_t epoch, uint64_t blocks, float *out, int *status, const PeerXchg &px,
+                                 unsigned char *smem, uint64_t *bars) {
+    const int lane = threadIdx.x;
+    if (lane == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const unsigned long long t0 = global_ns(), limit = (unsigned long long)px.wait_ms * 1000000ull;
+    uint64_t base[2] = {0, 0};   // first word each buffer holds (even)
+    uint32_t held[2] = {0, 0};   // how many
+    uint32_t parity[2] = {0, 0};
+    auto fetch = [&](int b, uint64_t from) {  // one lane asks; the copy lands on bars[b]
+        base[b] = from & ~1ull;
+        const uint64_t left = blocks - base[b];
+        held[b] = (uint32_t)(left < UNSPLIT_WINDOW ? (left + 1) & ~1ull : UNSPLIT_WINDOW);  // a whole number of 16 bytes (the area has room)
+        if (lane == 0) {
+            // Generic-proxy reads of this buffer (the chain before) are ordered before the async-proxy write.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&bars[b], held[b] * 8);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             smem_addr(smem + (size_t)b * UNSPLIT_WINDOW * 8)),
+                         "l"(words + base[b]), "r"(held[b] * 8), "r"(smem_addr(&bars[b]))
+                         : "memory");
+        }
+    };
+    float s = 0.0f;
+    uint64_t pos = 0;  // next block to add
+    uint32_t fetches = 1;
+    int cur = 0;
+    bool failed = false;
+    fetch(0, 0);
+    while (true) {
+        if (!mbar_wait_bounded(&bars[cur], parity[cur])) {
+            failed = true;
+            break;
+        }
+        parity[cur] ^= 1;
+        // How far do this reduction's words reach from `pos`? Each lane looks at every 32nd word and, on
+        // the way, packs the low halves (the sums) to the front of the same buffer: word i of the
+        // buffer becomes float i. Four steps of 32 words are read before they are written; a step's
+        // floats land on words that earlier steps have read.
+        unsigned long long *wbuf = reinterpret_cast<unsigned long long *>(smem + (size_t)cur * UNSPLIT_WINDOW * 8);
+        float *fbuf = reinterpret_cast<float *>(wbuf);
+        const uint32_t k0 = (uint32_t)(pos - base[cur]), k_end = (uint32_t)(blocks - base[cur] < held[cur] ? blocks - base[cur] : held[cur]);
+        uint32_t first_gap = k_end;
+        for (uint32_t k = k0 & ~127u; k < k_end; k += 128) {
+            unsigned long long w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = k + u * 32 + lane < held[cur] ? wbuf[k + u * 32 + lane] : 0ull;
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t i = k + u * 32 + lane;
+                if (i < held[cur]) fbuf[i] = __uint_as_float((uint32_t)w[u]);
+                if (i >= k0 && i < k_end && (uint32_t)(w[u] >> 32) != epoch && i < first_gap) first_gap = i;
+            }
+            __syncwarp();
+        }
+        first_gap = __reduce_min_sync(0xffffffffu, first_gap);
+        const uint64_t reach = base[cur] + first_gap;
+        const bool complete = reach == blocks;
+        if (complete && lane == 0) peer_trace(px, 2);  // every rank's part has arrived
+        if (!complete) {
+            if (__any_sync(0xffffffffu, global_ns() - t0 > limit)) {
+                failed = true;
+                break;
+            }
+            fetch(cur ^ 1, reach);  // in flight while the chain below runs
+            ++fetches;
+        }
+        // chain floats k0 .. first_gap: singly up to a 16-byte boundary, then staged
+        uint32_t k = k0;
+        for (; k < first_gap && (k & 3) != 0; ++k) s = __fadd_rn(s, fbuf[k]);
+        if (k < first_gap) s = chain_staged(fbuf + k, first_gap - k, s);
+        pos = reach;
+        if (complete) break;
+        cur ^= 1;
+    }
+    if (failed) {
+        // Nothing is on its way into shared memory here: either the one copy in flight had its bounded
+        // chance and never landed, or time ran out between two copies.
+        if (lane == 0) {
+            *(volatile int *)status = STATUS_PEER_WAIT_EXPIRED;
+            __threadfence_system();
+        }
+        return;
+    }
+    if (px.divide_by != 0.0f) s = __fdiv_rn(s, px.divide_by);
+    if (lane == 0) {
+        out[0] = s;
+        peer_trace(px, 3);
+        if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * PEER_TRACE_WORDS + 13] = fetches;
+    }
+}
+
 // `launch_no`: this kernel's number among the device's chained reductions (see combiner_begin).
 __device__ void ordered_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t blocks, float *out, int *status,
-                                 const PeerXchg &px, float *stage, unsigned long long *done, uint32_t launch_no) {
-    combiner_begin(done, launch_no, status);
-    ordered_combiner_body(mailbox, epoch, blocks, out, status, px, stage);
+                                 const PeerXchg &px, float *stage, unsigned long long *done, uint32_t launch_no, uint32_t lag, uint64_t *bars) {
+    combiner_begin(done, launch_no, status, lag);
+    if (px.blocks_total != 0) unsplit_combiner(mailbox, epoch, blocks, out, status, px, reinterpret_cast<unsigned char *>(stage), bars);
+    else ordered_combiner_body(mailbox, epoch, blocks, out, status, px, stage);
     __syncwarp();
     if (threadIdx.x == 0) combiner_end(done, launch_no);
 }
@@ -552,14 +674,14 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
         if (px.blocks_total != 0) {  // unsplit order: chain the whole tensor's block sums out of this rank's own window
             const unsigned long long *mine = own_window(px);
             return ordered_combiner(mine + PEER_BLOCK_AREA_WORD + (size_t)(px.epoch % PEER_GENERATIONS) * PEER_BLOCKS_MAX, px.epoch, px.blocks_total, dst,
-                                    status, px, ring, done, epoch);
+                                    status, px, ring, done, epoch, ordered >> 8, bars);
         }
-        return ordered_combiner(mailbox, epoch, blocks, dst, status, px, ring, done, epoch);
+        return ordered_combiner(mailbox, epoch, blocks, dst, status, px, ring, done, epoch, ordered >> 8, bars);
     }
     // `ordered`: what came before in the stream may have written this kernel's input, so it waits for
     // that to complete like every other kernel. Otherwise (the kernel before is a reduction of other
     // buffers) a worker needs nothing from it and starts streaming at once.
-    if (!FUSED || ordered) ordered_start();
+    if (!FUSED || (ordered & 1)) ordered_start();
     else launch_dependents();
     const bool unsplit = FUSED && px.blocks_total != 0;
     if (unsplit && blockIdx.x == 1) return block_forwarder(mailbox, epoch, blocks, status, px);
@@ -575,10 +697,11 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
     const uint32_t m = (uint32_t)(len - lo < SUM_BLOCK ? len - lo : SUM_BLOCK);
     const float *p = x + row * len + lo;
     const uint32_t chunks = m / CHUNK;
+    const uint64_t once = read_once_policy();
     if (lane == 0) {
         for (uint32_t c = 0; c < STAGES && c < chunks; ++c) {
             mbar_expect_tx(&bars[c], CHUNK_BYTES);
-            bulk_load(ring + (size_t)c * CHUNK, p + (size_t)c * CHUNK, CHUNK_BYTES, &bars[c]);
+            bulk_load(ring + (size_t)c * CHUNK, p + (size_t)c * CHUNK, CHUNK_BYTES, &bars[c], once);
         }
     }
     float s = 0.0f;
@@ -605,7 +728,7 @@ __global__ void __launch_bounds__(32) sum_rows_tma_kernel(const float *__restric
         __syncwarp();  // every lane is done reading this stage before it is refilled
         if (lane == 0 && c + STAGES < chunks) {
             mbar_expect_tx(&bars[st], CHUNK_BYTES);
-            bulk_load(ring + (size_t)st * CHUNK, p + (size_t)(c + STAGES) * CHUNK, CHUNK_BYTES, &bars[st]);
+            bulk_load(ring + (size_t)st * CHUNK, p + (size_t)(c + STAGES) * CHUNK, CHUNK_BYTES, &bars[st], once);
         }
     }
     // What is left of the block (fewer than CHUNK elements) continues the same slots with loads.
@@ -1035,8 +1158,8 @@ __device__ void max_combiner_body(const unsigned long long *mailbox, uint32_t ep
 }
 
 __device__ void max_combiner(const unsigned long long *mailbox, uint32_t epoch, uint64_t segs, const int64_t *seg_pos, float *out_v, int64_t *out_i,
-                             int64_t idx_offset, int *status, const PeerXchg &px, unsigned long long *done) {
-    combiner_begin(done, epoch, status);  // same ordering rules as the sum's combiner
+                             int64_t idx_offset, int *status, const PeerXchg &px, unsigned long long *done, uint32_t lag) {
+    combiner_begin(done, epoch, status, lag);  // same ordering rules as the sum's combiner
     max_combiner_body(mailbox, epoch, segs, seg_pos, out_v, out_i, idx_offset, status, px);
     __syncthreads();
     if (threadIdx.x == 0) combiner_end(done, epoch);
@@ -1065,8 +1188,8 @@ __global__ void __launch_bounds__(MAX_CTA) max_rows_kernel(const float *__restri
                                                            int64_t *__restrict__ out_i, int64_t idx_offset, const __grid_constant__ MaxFused fused) {
     constexpr int PER_CTA = MAX_CTA / TPT;
     if (TPT == MAX_CTA && fused.mailbox != nullptr && blockIdx.x == 0)
-        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px, fused.done);
-    if (TPT == MAX_CTA && fused.mailbox != nullptr && !fused.ordered) launch_dependents();
+        return max_combiner(fused.mailbox, fused.epoch, segs, out_i, fused.final_v, fused.final_i, fused.final_offset, fused.status, fused.px, fused.done, (uint32_t)fused.ordered >> 8);
+    if (TPT == MAX_CTA && fused.mailbox != nullptr && !(fused.ordered & 1)) launch_dependents();
     else ordered_start();
     const uint64_t cta = (TPT == MAX_CTA && fused.mailbox != nullptr) ? blockIdx.x - 1 : blockIdx.x;
     const uint64_t t = cta * PER_CTA + threadIdx.x / TPT;
@@ -1365,7 +1488,7 @@ bool staged_kernels_ready(int device) {
            cudaFuncSetAttribute(sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                 (int)ring_bytes(RINGS[I].stages, RINGS[I].chunk)) == cudaSuccess &&                                    \
            cudaFuncSetAttribute(sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                (int)ring_bytes(RINGS[I].stages, RINGS[I].chunk)) == cudaSuccess;
+                                (int)fused_smem(RINGS[I].stages, RINGS[I].chunk, true)) == cudaSuccess;
         B200_RING_ATTR(0) B200_RING_ATTR(1) B200_RING_ATTR(2) B200_RING_ATTR(3) B200_RING_ATTR(4)
 #undef B200_RING_ATTR
         ok[device] = good &&
@@ -1418,7 +1541,7 @@ static_assert((PEER_BLOCK_AREA_WORD + (size_t)PEER_GENERATIONS * PEER_BLOCKS_MAX
 struct PeerWindows {
     std::mutex mu;
     unsigned long long *local[64] = {};
-    unsigned long long *trace[64] = {};  // PEER_TRACE_RECORDS x 4 words per device
+    unsigned long long *trace[64] = {};  // PEER_TRACE_RECORDS x PEER_TRACE_WORDS words per device
     cudaIpcMemHandle_t local_handle[64] = {};
     std::vector<std::pair<cudaIpcMemHandle_t, void *>> opened[64];
     PeerXchg attached[64] = {};
@@ -1445,10 +1568,10 @@ cudaError_t peer_window_export(int device, void *handle, cudaStream_t s) {
     }
     if (!w.trace[device]) {
         void *t = nullptr;
-        if ((e = cudaMalloc(&t, (size_t)PEER_TRACE_RECORDS * 4 * 8)) != cudaSuccess) return e;
+        if ((e = cudaMalloc(&t, (size_t)PEER_TRACE_RECORDS * PEER_TRACE_WORDS * 8)) != cudaSuccess) return e;
         w.trace[device] = (unsigned long long *)t;
     }
-    if ((e = cudaMemsetAsync(w.trace[device], 0, (size_t)PEER_TRACE_RECORDS * 4 * 8, s)) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(w.trace[device], 0, (size_t)PEER_TRACE_RECORDS * PEER_TRACE_WORDS * 8, s)) != cudaSuccess) return e;
     w.attached[device] = PeerXchg{};
     // Everything this device has in flight finishes before the window is cleared, and the clearing
     // finishes before the handle leaves this call: no peer can write before it holds the handle.
@@ -1497,13 +1620,13 @@ cudaError_t peer_window_attach(int device, uint32_t rank, uint32_t world, const 
     return cudaSuccess;
 }
 
-// Copies the trace records of `device`'s own window (PEER_TRACE_RECORDS x 4 words) to the host.
+// Copies the trace records of `device` (PEER_TRACE_RECORDS x PEER_TRACE_WORDS words) to the host.
 cudaError_t peer_trace_read(int device, unsigned long long *out, cudaStream_t s) {
     if (device < 0 || device >= 64 || !out) return cudaErrorInvalidValue;
     PeerWindows &w = peer_windows();
     std::lock_guard<std::mutex> lock(w.mu);
     if (!w.trace[device]) return cudaErrorInvalidValue;
-    cudaError_t e = cudaMemcpyAsync(out, w.trace[device], (size_t)PEER_TRACE_RECORDS * 4 * 8, cudaMemcpyDeviceToHost, s);
+    cudaError_t e = cudaMemcpyAsync(out, w.trace[device], (size_t)PEER_TRACE_RECORDS * PEER_TRACE_WORDS * 8, cudaMemcpyDeviceToHost, s);
     return e == cudaSuccess ? cudaStreamSynchronize(s) : e;
 }
 
@@ -1548,6 +1671,16 @@ bool may_overlap(const LaunchChain *c, const float *x, uint64_t n, const void *o
             if (o && (const char *)o >= open->in_lo && (const char *)o < open->in_hi) return false;  // we write into its input
     }
     return true;
+}
+
+// How many launches back the combiner whose end a combiner awaits before it lets its successor start
+// (see combiner_begin): 2, or 1 with PYTORCHES_B200_CHAIN_LAG=1 in the environment (a diagnostic).
+uint32_t chain_lag() {
+    static const uint32_t lag = [] {
+        const char *e = getenv("PYTORCHES_B200_CHAIN_LAG");
+        return e && e[0] == '1' ? 1u : 2u;
+    }();
+    return lag;
 }
 
 // `early`: this launch was allowed to start before `prev`'s newest one completed, so that one stays on the list.
@@ -1600,8 +1733,8 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
     if (ring == I) {                                                                                                                        \
         if (mailbox)                                                                                                                        \
             B200_LAUNCH_ORDERED((sum_rows_tma_kernel<true, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks + (unsplit ? 2 : 1), 32,       \
-                                ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, o, status, mailbox, epoch,           \
-                                px ? *px : no_peers, early ? 0u : 1u, done);                                                                \
+                                fused_smem(RINGS[I].stages, RINGS[I].chunk, unsplit), s, x, tasks, len, blocks, o, status, mailbox, epoch,  \
+                                px ? *px : no_peers, (early ? 0u : 1u) | chain_lag() << 8, done);                                                                \
         else                                                                                                                                \
             B200_LAUNCH_ORDERED((sum_rows_tma_kernel<false, RINGS[I].stages, RINGS[I].chunk>), (unsigned)tasks, 32,                         \
                                 ring_bytes(RINGS[I].stages, RINGS[I].chunk), s, x, tasks, len, blocks, dst, status,                         \
@@ -1678,7 +1811,7 @@ cudaError_t launch_reduce_local(ReduceKind kind, const float *x, uint64_t outer,
         unsigned long long *mailbox = status ? mailbox_for(device, s, &epoch, &done) : nullptr;
         if (mailbox) {
             early = may_overlap(prev, x, len, ov, oi);
-            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers, early ? 0 : 1, done};
+            fused = MaxFused{mailbox, epoch, ov, oi, idx_offset, status, px ? *px : no_peers, (int)((early ? 0u : 1u) | chain_lag() << 8), done};
             grid += 1;
             *peer_done = px != nullptr;
         }

@@ -168,12 +168,14 @@ class ShardGroup:
         return out
 
     def peer_trace(self) -> np.ndarray:
-        """[64, 4] device-clock readings (ns) of this rank's last 64 reductions with an in-kernel exchange,
-        row (seq % 0xfffffffe + 1) % 64: unused, own part complete, every rank's part arrived, result
-        written (``pytorches_b200_peer_trace``; all zero unless PYTORCHES_B200_PEER_TRACE=1). Synchronizes the device's stream."""
+        """[64, 16] device-clock readings (ns) of this rank's last 64 reductions with an in-kernel exchange,
+        row (seq % 0xfffffffe + 1) % 64: [1] own part complete, [2] every rank's part arrived, [3] result
+        written; for sums in unsplit order also [13], how many bulk copies of the block sums the combiner
+        needed (``pytorches_b200_peer_trace``; all zero unless PYTORCHES_B200_PEER_TRACE=1).
+        Synchronizes the device's stream."""
         fn = self.device.plugin.lib.pytorches_b200_peer_trace
         fn.restype, fn.argtypes = C.c_int32, [C.c_uint32, C.c_void_p]
-        out = np.zeros((64, 4), dtype=np.uint64)
+        out = np.zeros((64, 16), dtype=np.uint64)
         self.device.plugin.check(fn(self.device.index, out.ctypes.data), "peer trace")
         return out
 
