@@ -52,10 +52,10 @@ ORACLE_SO = os.path.join(ROOT, "oracle", "_build", "pytorches_plugin_cpuref.so")
 METRIC = "f32 elementwise/reduce HBM GB/s"
 ROTATE_BYTES = 512 << 20  # an op's input was last touched at least this many bytes of traffic ago
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused SUM_AXIS launch, from an ncu capture of a
-# 2^26-element launch (268.495 MB read, 5.07 MB written back from L2): the read part grows with the
+# 2^26-element launch (268.53 MB read, 4.05 MB written back from L2): the read part grows with the
 # element count and is scaled to this workload's launch, the write part is kept.
-NCU_READ_BYTES_PER_ELEMENT = 268.495e6 / (1 << 26)
-NCU_WRITE_BYTES_PER_LAUNCH = 5.07e6
+NCU_READ_BYTES_PER_ELEMENT = 268.531712e6 / (1 << 26)
+NCU_WRITE_BYTES_PER_LAUNCH = 4.047104e6
 
 
 def workload_config(world: int) -> dict:

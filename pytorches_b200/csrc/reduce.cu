@@ -526,58 +526,56 @@ __device__ void unsplit_combiner(const unsigned long long *words, uint32_t epoch
     }
     __syncwarp();
     const unsigned long long t0 = global_ns(), limit = (unsigned long long)px.wait_ms * 1000000ull;
-    uint64_t base[2] = {0, 0};   // first word each buffer holds (even)
-    uint32_t held[2] = {0, 0};   // how many
-    uint32_t parity[2] = {0, 0};
-    auto fetch = [&](int b, uint64_t from) {  // one lane asks; the copy lands on bars[b]
-        base[b] = from & ~1ull;
-        const uint64_t left = blocks - base[b];
-        held[b] = (uint32_t)(left < UNSPLIT_WINDOW ? (left + 1) & ~1ull : UNSPLIT_WINDOW);  // a whole number of 16 bytes (the area has room)
+    // Copy number f lands in buffer f & 1 on bars[f & 1], whose phase it completes is (f >> 1) & 1.
+    auto fetch = [&](uint32_t f, uint64_t from, uint64_t &first, uint32_t &count) {  // one lane asks
+        first = from & ~1ull;  // 16-byte aligned
+        const uint64_t left = blocks - first;
+        count = (uint32_t)(left < UNSPLIT_WINDOW ? (left + 1) & ~1ull : UNSPLIT_WINDOW);  // a whole number of 16 bytes (the area has room)
         if (lane == 0) {
             // Generic-proxy reads of this buffer (the chain before) are ordered before the async-proxy write.
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(&bars[b], held[b] * 8);
+            mbar_expect_tx(&bars[f & 1], count * 8);
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                             smem_addr(smem + (size_t)b * UNSPLIT_WINDOW * 8)),
-                         "l"(words + base[b]), "r"(held[b] * 8), "r"(smem_addr(&bars[b]))
+                             smem_addr(smem + (size_t)(f & 1) * UNSPLIT_WINDOW * 8)),
+                         "l"(words + first), "r"(count * 8), "r"(smem_addr(&bars[f & 1]))
                          : "memory");
         }
     };
     float s = 0.0f;
-    uint64_t pos = 0;  // next block to add
-    uint32_t fetches = 1;
-    int cur = 0;
+    uint64_t pos = 0;            // next block to add
+    uint64_t base = 0, base_next = 0;  // first word the landed / the requested copy holds
+    uint32_t held = 0, held_next = 0;  // how many
     bool failed = false;
-    fetch(0, 0);
+    uint32_t f = 0;              // the copy being waited for
+    fetch(0, 0, base, held);
     while (true) {
-        if (!mbar_wait_bounded(&bars[cur], parity[cur])) {
+        if (!mbar_wait_bounded(&bars[f & 1], (f >> 1) & 1)) {
             failed = true;
             break;
         }
-        parity[cur] ^= 1;
         // How far do this reduction's words reach from `pos`? Each lane looks at every 32nd word and, on
         // the way, packs the low halves (the sums) to the front of the same buffer: word i of the
         // buffer becomes float i. Four steps of 32 words are read before they are written; a step's
         // floats land on words that earlier steps have read.
-        unsigned long long *wbuf = reinterpret_cast<unsigned long long *>(smem + (size_t)cur * UNSPLIT_WINDOW * 8);
+        unsigned long long *wbuf = reinterpret_cast<unsigned long long *>(smem + (size_t)(f & 1) * UNSPLIT_WINDOW * 8);
         float *fbuf = reinterpret_cast<float *>(wbuf);
-        const uint32_t k0 = (uint32_t)(pos - base[cur]), k_end = (uint32_t)(blocks - base[cur] < held[cur] ? blocks - base[cur] : held[cur]);
+        const uint32_t k0 = (uint32_t)(pos - base), k_end = (uint32_t)(blocks - base < held ? blocks - base : held);
         uint32_t first_gap = k_end;
         for (uint32_t k = k0 & ~127u; k < k_end; k += 128) {
             unsigned long long w[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) w[u] = k + u * 32 + lane < held[cur] ? wbuf[k + u * 32 + lane] : 0ull;
+            for (int u = 0; u < 4; ++u) w[u] = k + u * 32 + lane < held ? wbuf[k + u * 32 + lane] : 0ull;
             __syncwarp();
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const uint32_t i = k + u * 32 + lane;
-                if (i < held[cur]) fbuf[i] = __uint_as_float((uint32_t)w[u]);
+                if (i < held) fbuf[i] = __uint_as_float((uint32_t)w[u]);
                 if (i >= k0 && i < k_end && (uint32_t)(w[u] >> 32) != epoch && i < first_gap) first_gap = i;
             }
             __syncwarp();
         }
         first_gap = __reduce_min_sync(0xffffffffu, first_gap);
-        const uint64_t reach = base[cur] + first_gap;
+        const uint64_t reach = base + first_gap;
         const bool complete = reach == blocks;
         if (complete && lane == 0) peer_trace(px, 2);  // every rank's part has arrived
         if (!complete) {
@@ -585,8 +583,7 @@ __device__ void unsplit_combiner(const unsigned long long *words, uint32_t epoch
                 failed = true;
                 break;
             }
-            fetch(cur ^ 1, reach);  // in flight while the chain below runs
-            ++fetches;
+            fetch(f + 1, reach, base_next, held_next);  // in flight while the chain below runs
         }
         // chain floats k0 .. first_gap: singly up to a 16-byte boundary, then staged
         uint32_t k = k0;
@@ -594,7 +591,9 @@ __device__ void unsplit_combiner(const unsigned long long *words, uint32_t epoch
         if (k < first_gap) s = chain_staged(fbuf + k, first_gap - k, s);
         pos = reach;
         if (complete) break;
-        cur ^= 1;
+        ++f;
+        base = base_next;
+        held = held_next;
     }
     if (failed) {
         // Nothing is on its way into shared memory here: either the one copy in flight had its bounded
@@ -609,7 +608,7 @@ __device__ void unsplit_combiner(const unsigned long long *words, uint32_t epoch
     if (lane == 0) {
         out[0] = s;
         peer_trace(px, 3);
-        if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * PEER_TRACE_WORDS + 13] = fetches;
+        if (px.trace) px.trace[(size_t)(px.epoch % PEER_TRACE_RECORDS) * PEER_TRACE_WORDS + 13] = f + 1;
     }
 }
 

@@ -94,6 +94,20 @@ def test_single_rank_group_sums_in_unsplit_order(b200, n):
         assert g.mean(t, n, 0).numpy().tobytes() == t.mean().numpy().tobytes()
 
 
+def test_unsplit_order_with_more_blocks_than_one_copy_holds(b200):
+    """4797 blocks (an odd number, a ragged last block): the combiner's bulk copies hold 4096 words, so
+    the window over the block sums has to move; the bits must still be SUM_AXIS's."""
+    n = 65536 * 4096 + 65536 * 700 + 3
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange(), b200.last_error()
+    assert g.unsplit_order(n)
+    t = Tensor.rand_uniform_on([n], 21, -1.0, 1.0, dev)
+    for _ in range(3):
+        assert g.sum(t, 0, n).numpy().tobytes() == t.sum().numpy().tobytes()
+        assert g.mean(t, n, 0).numpy().tobytes() == t.mean().numpy().tobytes()
+
+
 def test_unsplit_order_needs_whole_blocks(b200):
     import ctypes as C
 
