@@ -215,7 +215,8 @@ def test_sum_axis_bit_exact(oracle, b200, shape):
         assert np.all(np.abs(got - ref) <= tol * np.maximum(scale, 1e-30))
 
 
-@pytest.mark.parametrize("shape", [(1000,), (70_001,), (3, 200_000), (100_000, 3), (2, 600, 5), (64, 4096), (1 << 22,), (128, 2048), (5, 16385)])
+@pytest.mark.parametrize("shape", [(1000,), (70_001,), (3, 200_000), (100_000, 3), (2, 600, 5), (64, 4096), (1 << 22,), (128, 2048), (5, 16385),
+                                   ((1 << 22) + 65536 * 3 + 4101,), ((1 << 23) + 7,)])
 def test_max_argmax_match_oracle(oracle, b200, shape):
     n = int(np.prod(shape))
     x = (np.round(lcg_data(n, 11) * 64) / 64).astype(np.float32)  # plenty of ties
@@ -229,7 +230,7 @@ def test_max_argmax_match_oracle(oracle, b200, shape):
 
 
 def test_argmax_all_minus_inf_and_nan_first(oracle, b200):
-    for n in (5, 4096, 70_000):
+    for n in (5, 4096, 70_000, (1 << 22) + 65536 + 12):  # the last one takes the staged kernel for one long row
         x = np.full(n, -np.inf, dtype=np.float32)
         got, want = both(oracle, b200, op.ARGMAX_AXIS, [0], [(x, (n,), (1,))], (), DTYPE_I64)
         assert got[0] == want[0] == 0
