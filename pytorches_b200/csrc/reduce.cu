@@ -199,11 +199,6 @@ __device__ __forceinline__ unsigned long long ld_mailbox(const unsigned long lon
     return v;
 }
 
-__device__ __forceinline__ unsigned long long ld_mailbox_sys(const unsigned long long *p) {
-    unsigned long long v;
-    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __device__ __forceinline__ bool vi_better(float v, uint64_t i, float bv, uint64_t bi);
 
