@@ -160,6 +160,34 @@ def test_a_peer_that_never_answers_is_a_reported_error_not_a_hang(b200):
     del out
 
 
+def test_unsplit_sum_whose_peer_never_sends_its_blocks_is_a_reported_error(b200):
+    """The same for a sum in unsplit order: the combiner's copies of the block sums keep coming back
+    without the second rank's words; after the time limit the failure is recorded, not waited out."""
+    import ctypes as C
+
+    dev = Device(b200, 0)
+    g = ShardGroup(dev, 0, 1)
+    assert g.enable_peer_exchange()
+    lib = b200.lib
+    handle = C.create_string_buffer(64)
+    assert lib.pytorches_b200_peer_export(0, handle) == 0
+    assert lib.pytorches_b200_peer_attach(0, 0, 2, handle.raw + handle.raw, 50) == 0  # two ranks on paper, 50 ms of patience
+    fn = lib.pytorches_b200_peer_sum_unsplit
+    fn.restype = C.c_int32
+    fn.argtypes = [C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_void_p]
+    n = 65536 * 40
+    t = Tensor.from_numpy(lcg_data(n, 5), dev)
+    out = Tensor.zeros_on([1], dev)
+    assert fn(0, t.buffer.ptr, n, 0, 2 * n, 0, g.peer_seq, out.buffer.ptr) == abi.STATUS_OK, b200.last_error()  # blocks 40..79 never come
+    g.advance_peer_seq(g.peer_seq + 1)
+    with pytest.raises(abi.PluginError) as err:
+        b200.synchronize(0)
+    assert err.value.status == abi.STATUS_INTERNAL and "peer" in str(err.value)
+    b200.synchronize(0)  # reported once; the device is usable
+    assert g.enable_peer_exchange()
+    assert g.sum(t, 0, n).numpy().tobytes() == t.sum().numpy().tobytes()
+
+
 def test_peer_reduce_needs_attached_windows(b200):
     import ctypes as C
 
