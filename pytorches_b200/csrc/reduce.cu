@@ -503,7 +503,9 @@ __device__ void ordered_combiner_body(const unsigned long long *mailbox, uint32_
 // UNSPLIT_WINDOW of them, 32 KiB) into shared memory; the warp finds how far the words of this
 // reduction reach without a gap, asks for the next copy into the other buffer, and chains what it
 // has out of shared memory meanwhile. After the last arrival that is at most two copies and one pass
-// of the chain. Waits are bounded: each copy by the barrier's try limit, the whole by px.wait_ms.
+// of the chain. A word is written by one aligned 8-byte store and a bulk copy moves aligned 16-byte
+// units, so a word is seen whole or not at all; a copy that overtakes a store only costs another
+// round. Waits are bounded: each copy by the barrier's try limit, the whole by px.wait_ms.
 constexpr uint32_t UNSPLIT_WINDOW = 4096;                                  // words per copy
 constexpr size_t UNSPLIT_SMEM = (size_t)2 * UNSPLIT_WINDOW * 8;            // two buffers
 // Dynamic shared memory of a fused launch: the workers' ring, and room for the unsplit combiner's buffers
