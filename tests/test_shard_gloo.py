@@ -203,3 +203,36 @@ def test_split_rows_covers_everything():
             for (s0, c0), (s1, _) in zip(spans, spans[1:]):
                 assert s0 + c0 == s1
             assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
+
+
+def test_unsplit_order_rule(oracle, monkeypatch):
+    """When may a sharded sum promise the bits of the unsplit sum? Pure host logic: every rank's shard must
+    be a run of whole 65536-element blocks (the last one may end ragged), hold at least one, and the
+    tensor must fit the window's block area; every rank must reach the same answer."""
+    from pytorches_b200.core import Device
+    from pytorches_b200.shard import ShardGroup
+
+    def answers(n, world):
+        out = []
+        for rank in range(world):
+            g = ShardGroup(Device(oracle, 0), rank, world)
+            g._peer_reduce = object()  # as if the in-kernel exchange were on
+            out.append(g.unsplit_order(n))
+        assert len(set(out)) == 1
+        return out[0]
+
+    B = 65536
+    for world in (1, 2, 4, 8):
+        assert answers(1 << 28, world)               # the benchmark's tensor
+        assert answers(B * world * 3, world)
+        assert not answers(0, world)
+        assert not answers((B << 14) + B, world)     # more blocks than the window holds
+    assert answers(B * 3 + 5, 1)                     # one rank: any length
+    assert not answers(B * 8 + 2 * 17, 2)            # rank 1 would start inside a block
+    assert not answers(B, 2)                         # rank 1 would hold nothing
+    assert not answers(B * 7, 2)                     # 3.5 blocks each
+    monkeypatch.setenv("PYTORCHES_B200_UNSPLIT_ORDER", "0")
+    assert not answers(1 << 28, 2)
+    g = ShardGroup(Device(oracle, 0), 0, 2)          # without the in-kernel exchange there is no such promise
+    monkeypatch.delenv("PYTORCHES_B200_UNSPLIT_ORDER")
+    assert not g.unsplit_order(1 << 28)
